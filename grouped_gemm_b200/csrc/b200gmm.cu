@@ -1,0 +1,293 @@
+// C-ABI entry points of libb200gmm (declared in include/b200gmm.h): argument
+// checks, TMA tensor-map construction and kernel launches.  No torch types, no
+// exceptions, no allocation: scratch comes from the caller.
+#include "../../include/b200gmm.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "gmm_kernel.cuh"
+
+namespace {
+
+using namespace b200gmm;
+
+std::atomic<int64_t> g_launches{0};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+struct DeviceInfo {
+  int sm_count = 0;
+  int cc_major = 0;
+  bool attrs_set = false;
+};
+
+// Per-device facts, looked up once.  Index = CUDA device ordinal.
+int device_info(DeviceInfo** out) {
+  static std::mutex mu;
+  static DeviceInfo infos[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200GMM_ECUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  DeviceInfo& d = infos[dev];
+  if (d.sm_count == 0) {
+    if (cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&d.cc_major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess)
+      return B200GMM_ECUDA;
+  }
+  if (d.cc_major != 10) return B200GMM_EDEVICE;
+  if (!d.attrs_set) {
+    const int smem = static_cast<int>(kSmemBytes);
+    if (cudaFuncSetAttribute(gmm_kernel<kNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(gmm_kernel<kNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(gmm_kernel<kTN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return B200GMM_ECUDA;
+    d.attrs_set = true;
+  }
+  *out = &d;
+  return B200GMM_OK;
+}
+
+// bf16 tensor map with 128-byte swizzle; dims/box innermost first.
+int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+               const uint32_t* box) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return B200GMM_ECUDA;
+  cuuint64_t gdim[3];
+  cuuint64_t gstride[2];
+  cuuint32_t gbox[3];
+  cuuint32_t estride[3] = {1, 1, 1};
+  uint64_t stride = 2;
+  for (int i = 0; i < rank; ++i) {
+    gdim[i] = dims[i];
+    gbox[i] = box[i];
+    stride *= dims[i];
+    if (i + 1 < rank) gstride[i] = stride;
+  }
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
+                        const_cast<void*>(base), gdim, gstride, gbox, estride,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200GMM_OK : B200GMM_ETENSORMAP;
+}
+
+int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int trans_b,
+                  Problem* p) {
+  if (trans_a && trans_b) return B200GMM_EINVAL;
+  if (z < 0 || tokens < 0 || d1 < 0 || n < 0) return B200GMM_EINVAL;
+  if (z > kMaxExperts) return B200GMM_ELIMIT;
+  if ((d1 % 8) != 0 || (n % 8) != 0) return B200GMM_EALIGN;
+  if (tokens >= (int64_t(1) << 31) - 256 || d1 >= (int64_t(1) << 31) - 256 ||
+      n >= (int64_t(1) << 31) - 256)
+    return B200GMM_ELIMIT;
+  p->mode = trans_a ? kTN : (trans_b ? kNT : kNN);
+  p->z = z;
+  p->tokens = tokens;
+  p->d1 = d1;
+  p->n = n;
+  // Upper bound on the tile count must fit the kernel's 32-bit tile index.
+  const int64_t nt = (n + kBlockN - 1) / kBlockN;
+  const int64_t row_tiles = trans_a ? int64_t(z) * ((d1 + kBlockM - 1) / kBlockM)
+                                    : (tokens / kBlockM + z);
+  if (row_tiles * nt >= (int64_t(1) << 31)) return B200GMM_ELIMIT;
+  return B200GMM_OK;
+}
+
+size_t round16(size_t x) { return (x + 15) & ~size_t(15); }
+
+}  // namespace
+
+extern "C" {
+
+int b200gmm_workspace_bytes(int z, size_t* out_bytes) {
+  if (out_bytes == nullptr || z < 0) return B200GMM_EINVAL;
+  if (z > kMaxExperts) return B200GMM_ELIMIT;
+  *out_bytes = round16(size_t(z) * sizeof(int64_t)) + 16;
+  return B200GMM_OK;
+}
+
+int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_sizes,
+                int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
+                int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
+                uint32_t* device_status, void* cuda_stream) {
+  Problem p;
+  int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, &p);
+  if (rc != B200GMM_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  if (z == 0) return B200GMM_OK;
+  if (batch_sizes == nullptr) return B200GMM_EINVAL;
+
+  // Degenerate shapes: nothing to multiply.  Only wgrad has output to define
+  // (zeros), and only when that output is non-empty.
+  if (p.mode == kTN) {
+    if (dim_a1 == 0 || n == 0) return B200GMM_OK;
+    if (c == nullptr) return B200GMM_EINVAL;
+    if (tokens == 0) {
+      if (cudaMemsetAsync(c, 0, size_t(z) * size_t(dim_a1) * size_t(n) * 2, stream) != cudaSuccess)
+        return B200GMM_ECUDA;
+      return B200GMM_OK;
+    }
+  } else {
+    if (tokens == 0 || n == 0) return B200GMM_OK;
+    if (c == nullptr) return B200GMM_EINVAL;
+    if (dim_a1 == 0) {
+      // k == 0: every product is an empty sum.
+      if (cudaMemsetAsync(c, 0, size_t(tokens) * size_t(n) * 2, stream) != cudaSuccess)
+        return B200GMM_ECUDA;
+      return B200GMM_OK;
+    }
+  }
+  if (a == nullptr || b == nullptr) return B200GMM_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(b) & 15) ||
+      (reinterpret_cast<uintptr_t>(c) & 15))
+    return B200GMM_EALIGN;
+
+  DeviceInfo* dev = nullptr;
+  rc = device_info(&dev);
+  if (rc != B200GMM_OK) return rc;
+
+  const int64_t* bs_dev = batch_sizes;
+  if (!batch_sizes_on_device) {
+    size_t need = 0;
+    b200gmm_workspace_bytes(z, &need);
+    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
+      return B200GMM_EWORKSPACE;
+    if (cudaMemcpyAsync(workspace, batch_sizes, size_t(z) * sizeof(int64_t), cudaMemcpyHostToDevice,
+                        stream) != cudaSuccess)
+      return B200GMM_ECUDA;
+    bs_dev = static_cast<const int64_t*>(workspace);
+  }
+
+  CUtensorMap map_a, map_b;
+  const uint64_t T = uint64_t(tokens), D1 = uint64_t(dim_a1), N = uint64_t(n), Z = uint64_t(z);
+  if (p.mode == kNN) {
+    const uint64_t da[2] = {D1, T};
+    const uint32_t ba[2] = {kBlockK, kBlockM};
+    const uint64_t db[3] = {N, D1, Z};
+    const uint32_t bb[3] = {64, kBlockK, 1};
+    if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
+      return rc;
+  } else if (p.mode == kNT) {
+    const uint64_t da[2] = {D1, T};
+    const uint32_t ba[2] = {kBlockK, kBlockM};
+    const uint64_t db[3] = {D1, N, Z};
+    const uint32_t bb[3] = {kBlockK, kBlockN, 1};
+    if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
+      return rc;
+  } else {
+    const uint64_t da[2] = {D1, T};
+    const uint64_t db[2] = {N, T};
+    const uint32_t bx[2] = {64, kBlockK};
+    if ((rc = encode_map(&map_a, a, 2, da, bx)) != 0 || (rc = encode_map(&map_b, b, 2, db, bx)) != 0)
+      return rc;
+  }
+
+  const dim3 grid(dev->sm_count), block(kThreads);
+  __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(c);
+  if (p.mode == kNN)
+    gmm_kernel<kNN><<<grid, block, kSmemBytes, stream>>>(map_a, map_b, cp, bs_dev, p, device_status);
+  else if (p.mode == kNT)
+    gmm_kernel<kNT><<<grid, block, kSmemBytes, stream>>>(map_a, map_b, cp, bs_dev, p, device_status);
+  else
+    gmm_kernel<kTN><<<grid, block, kSmemBytes, stream>>>(map_a, map_b, cp, bs_dev, p, device_status);
+  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200GMM_OK;
+}
+
+int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a1, int64_t n,
+                         int trans_a, int trans_b, int64_t* out_device, void* cuda_stream) {
+  if (trans_a && trans_b) return B200GMM_EINVAL;
+  if (z < 0 || dim_a1 < 0 || n < 0) return B200GMM_EINVAL;
+  if (z > kMaxExperts) return B200GMM_ELIMIT;
+  if (z == 0) return B200GMM_OK;
+  if (batch_sizes_device == nullptr || out_device == nullptr) return B200GMM_EINVAL;
+  Problem p;
+  p.mode = trans_a ? kTN : (trans_b ? kNT : kNN);
+  p.z = z;
+  p.tokens = 0;
+  p.d1 = dim_a1;
+  p.n = n;
+  fill_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(batch_sizes_device, p,
+                                                                            out_device);
+  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200GMM_OK;
+}
+
+int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z, int64_t tokens, int64_t dim_a1,
+                          int64_t n, int trans_a, int trans_b, int64_t* out, int64_t max_tiles,
+                          int64_t* n_tiles) {
+  Problem p;
+  const int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, &p);
+  if (rc != B200GMM_OK) return rc;
+  if (n_tiles == nullptr || (z > 0 && batch_sizes_host == nullptr)) return B200GMM_EINVAL;
+  int64_t count = 0;
+  int64_t start = 0;
+  for (int e = 0; e < z; ++e) {
+    int64_t v = batch_sizes_host[e] < 0 ? 0 : batch_sizes_host[e];
+    int64_t s = start < tokens ? start : tokens;
+    int64_t en = (start + v) < tokens ? (start + v) : tokens;
+    start += v;
+    const int tiles = expert_tiles(p, en - s);
+    for (int l = 0; l < tiles; ++l) {
+      if (out != nullptr && count < max_tiles) {
+        const Tile t = make_tile(p, e, l, static_cast<int>(s), static_cast<int>(en));
+        int64_t* o = out + count * 5;
+        o[0] = t.expert;
+        o[1] = t.row0;
+        o[2] = t.col0;
+        o[3] = t.valid_rows;
+        o[4] = (t.k_len + kBlockK - 1) / kBlockK;
+      }
+      ++count;
+    }
+  }
+  *n_tiles = count;
+  return B200GMM_OK;
+}
+
+int b200gmm_tile_shape(int trans_a, int trans_b, int* out3) {
+  if (out3 == nullptr || (trans_a && trans_b)) return B200GMM_EINVAL;
+  out3[0] = kBlockM;
+  out3[1] = kBlockN;
+  out3[2] = kBlockK;
+  return B200GMM_OK;
+}
+
+int64_t b200gmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* b200gmm_strerror(int code) {
+  switch (code) {
+    case B200GMM_OK: return "ok";
+    case B200GMM_EINVAL: return "invalid argument (null pointer, negative size, or trans_a and trans_b both set)";
+    case B200GMM_EALIGN: return "row lengths must be multiples of 8 bf16 elements and pointers 16-byte aligned";
+    case B200GMM_ELIMIT: return "too many experts (max 1024), too many tiles, or a dimension >= 2^31";
+    case B200GMM_EWORKSPACE: return "workspace missing, smaller than b200gmm_workspace_bytes(z), or not 16-byte aligned";
+    case B200GMM_ECUDA: return "a CUDA runtime or driver call failed";
+    case B200GMM_ETENSORMAP: return "cuTensorMapEncodeTiled rejected a tensor (address, stride or extent)";
+    case B200GMM_EDEVICE: return "current device is not compute capability 10.x (B200, sm_100a)";
+    case B200GMM_ETIMEOUT: return "a bounded wait inside the kernel gave up (device status word)";
+    default: return "unknown b200gmm error code";
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,60 @@
+"""Build libb200gmm.so in-tree with nvcc for sm_100a.
+
+Usage: ``python -m grouped_gemm_b200.csrc.build [--force] [--verbose]``.
+The library has no torch dependency; it links the shared CUDA runtime so that a
+process that already loaded torch's libcudart shares one runtime with it.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+SOURCES = ["b200gmm.cu"]
+HEADERS = ["gmm_kernel.cuh", "ptx.cuh", "schedule.cuh", os.path.join(ROOT, "include", "b200gmm.h")]
+LIB = os.path.join(HERE, "libb200gmm.so")
+
+
+def _nvcc():
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.exists(cand):
+            return cand
+    raise RuntimeError("nvcc not found; set NVCC or put it on PATH")
+
+
+def is_stale():
+    if not os.path.exists(LIB):
+        return True
+    built = os.path.getmtime(LIB)
+    deps = [os.path.join(HERE, s) for s in SOURCES] + [
+        h if os.path.isabs(h) else os.path.join(HERE, h) for h in HEADERS
+    ]
+    return any(os.path.getmtime(d) > built for d in deps)
+
+
+def build(force=False, verbose=False):
+    """Compile the library if it is missing or older than its sources."""
+    if not force and not is_stale():
+        return LIB
+    nvcc = _nvcc()
+    cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
+    cmd = [
+        nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+        "-shared", "-cudart", "shared", "-Xcompiler", "-fPIC",
+        "-Xlinker", "-rpath," + cuda_lib,
+        "-o", LIB,
+    ] + [os.path.join(HERE, s) for s in SOURCES]
+    if verbose:
+        cmd.insert(1, "-Xptxas")
+        cmd.insert(2, "-v")
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+    if res.returncode != 0:
+        raise RuntimeError("nvcc failed building libb200gmm.so")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))

@@ -1,0 +1,357 @@
+// The persistent grouped-GEMM kernel for sm_100a.
+//
+// One CTA per SM walks a static round-robin share of all experts' output tiles
+// (schedule.cuh).  Inside a CTA three roles run concurrently:
+//   warp 0      TMA producer: fills a kStages-deep ring of {A tile, B tile} in
+//               shared memory (128-byte swizzle), one mbarrier per stage;
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (bf16 x bf16 -> fp32 in
+//               TMEM), commits each stage back to the producer and each finished
+//               accumulator to the epilogue; two 256-column accumulators alternate
+//               so the epilogue of tile i overlaps the main loop of tile i+1;
+//   warps 2-5   epilogue: tcgen05.ld the accumulator, round to bf16, store the
+//               rows that exist (ragged last tile of an expert is masked).
+//
+// This replaces the CUTLASS GemmGrouped instantiations of the reference
+// (csrc/grouped_gemm.cu:38-81, :324-371), its argument-fill kernel
+// (csrc/fill_arguments.cuh:34-98) and the k==0 zero-fill kernels
+// (csrc/fill_arguments.cuh:100-131) with a single launch.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+#include "schedule.cuh"
+
+namespace b200gmm {
+
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kMaxExperts = 1024;
+constexpr uint32_t kTmemCols = 512;
+
+constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;  // 16 KiB
+constexpr uint32_t kBTileBytes = kBlockN * kBlockK * 2;  // 32 KiB
+constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+constexpr uint32_t kBoxBytes = 64 * kBlockK * 2;  // one 64-wide MN-major TMA box: 8 KiB
+
+struct __align__(8) SmemTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  int row_start[kMaxExperts + 1];
+  int tile_start[kMaxExperts + 1];
+};
+
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(SmemTail);
+
+// Exclusive prefix sums of batch_sizes (rows) and of per-expert tile counts,
+// by one warp, 32 experts per step with a running carry.  Rows are clamped to
+// `tokens` so that a bad batch_sizes can never push a store out of bounds.
+__device__ __forceinline__ void scan_batch_sizes(const Problem& p, const int64_t* batch_sizes,
+                                                 int* row_start, int* tile_start, uint32_t* status,
+                                                 int lane) {
+  int64_t carry_rows = 0;
+  int carry_tiles = 0;
+  uint32_t flags = 0;
+  for (int base = 0; base < p.z; base += 32) {
+    const int e = base + lane;
+    int64_t v = (e < p.z) ? batch_sizes[e] : 0;
+    if (v < 0) { v = 0; flags |= 0x2u; }
+    int64_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    int64_t start = carry_rows + incl - v;
+    int64_t end = start + v;
+    if (end > p.tokens) { flags |= 0x4u; end = p.tokens; }
+    if (start > p.tokens) start = p.tokens;
+    const int tiles = (e < p.z) ? expert_tiles(p, end - start) : 0;
+    int incl_t = tiles;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl_t, d);
+      if (lane >= d) incl_t += up;
+    }
+    if (e < p.z) {
+      row_start[e] = static_cast<int>(start);
+      tile_start[e] = carry_tiles + incl_t - tiles;
+    }
+    carry_rows += __shfl_sync(0xffffffffu, incl, 31);
+    carry_tiles += __shfl_sync(0xffffffffu, incl_t, 31);
+  }
+  if (lane == 0) {
+    row_start[p.z] = static_cast<int>(carry_rows < p.tokens ? carry_rows : p.tokens);
+    tile_start[p.z] = carry_tiles;
+  }
+  flags = __reduce_or_sync(0xffffffffu, flags);
+  if (flags != 0u && lane == 0 && status != nullptr && blockIdx.x == 0) atomicOr(status, flags);
+}
+
+// Round-robin walk over this CTA's tiles; every role keeps its own copy.
+struct TileWalker {
+  const Problem& p;
+  const int* row_start;
+  const int* tile_start;
+  int t;
+  int e;
+  int total;
+  int step;
+  __device__ TileWalker(const Problem& p_, const int* rs, const int* ts)
+      : p(p_), row_start(rs), tile_start(ts), t(blockIdx.x), e(0), total(ts[p_.z]), step(gridDim.x) {}
+  __device__ __forceinline__ bool next(Tile* out) {
+    if (t >= total) return false;
+    while (t >= tile_start[e + 1]) ++e;
+    *out = make_tile(p, e, t - tile_start[e], row_start[e], row_start[e + 1]);
+    t += step;
+    return true;
+  }
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+           __nv_bfloat16* __restrict__ c, const int64_t* __restrict__ batch_sizes, const Problem p,
+           uint32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
+  uint8_t* smem = smem_raw + pad;  // 1024-byte aligned: required by the 128-byte swizzle
+  const uint32_t stage_base = raw_addr + pad;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + size_t(kStages) * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile uint32_t* abort_flag = &tail->abort_flag;
+
+  // ------------------------------------------------------------ prologue
+  if (warp == 0) {
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_a);
+      ptx::prefetch_tensormap(&map_b);
+      for (int s = 0; s < kStages; ++s) {
+        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+        ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+      }
+      for (int i = 0; i < 2; ++i) {
+        ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[i]), 1);
+        ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[i]), 4);
+      }
+      tail->abort_flag = 0u;
+      ptx::fence_mbar_init();
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), kTmemCols);
+    ptx::tmem_relinquish();
+  } else if (warp == 2) {
+    scan_batch_sizes(p, batch_sizes, tail->row_start, tail->tile_start, status, lane);
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = tail->tmem_base;
+
+  constexpr bool kAMn = (MODE == kTN);             // A operand MN-major (wgrad reads a^T)
+  constexpr bool kBMn = (MODE == kNN || MODE == kTN);  // B operand MN-major
+  constexpr uint32_t kIdesc = ptx::make_idesc_bf16(kBlockM, kBlockN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+
+  if (warp == 0) {
+    // ---------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      TileWalker walk(p, tail->row_start, tail->tile_start);
+      Tile t;
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      while (ok && walk.next(&t)) {
+        const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t bar = ptx::smem_u32(&tail->full[s]);
+          const uint32_t sa = stage_base + s * kStageBytes;
+          const uint32_t sb = sa + kATileBytes;
+          ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+          const int k0 = kb * kBlockK;
+          if (MODE == kNN) {
+            ptx::tma_load_2d(sa, &map_a, bar, k0, t.row0);
+#pragma unroll
+            for (int j = 0; j < kBlockN / 64; ++j)
+              ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, bar, t.col0 + j * 64, k0, t.expert);
+          } else if (MODE == kNT) {
+            ptx::tma_load_2d(sa, &map_a, bar, k0, t.row0);
+            ptx::tma_load_3d(sb, &map_b, bar, k0, t.col0, t.expert);
+          } else {
+            const int r0 = t.k_row0 + k0;
+#pragma unroll
+            for (int j = 0; j < kBlockM / 64; ++j)
+              ptx::tma_load_2d(sa + j * kBoxBytes, &map_a, bar, t.row0 + j * 64, r0);
+#pragma unroll
+            for (int j = 0; j < kBlockN / 64; ++j)
+              ptx::tma_load_2d(sb + j * kBoxBytes, &map_b, bar, t.col0 + j * 64, r0);
+          }
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- MMA issuer
+    TileWalker walk(p, tail->row_start, tail->tile_start);
+    Tile t;
+    uint32_t s = 0, ph = 0, it = 0;
+    bool ok = true;
+    while (ok && walk.next(&t)) {
+      const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+      if (nkb == 0) continue;  // empty wgrad expert: the epilogue writes zeros
+      const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
+      ++it;
+      if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[ab]), aph ^ 1u, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const uint32_t d_tmem = tmem_base + ab * kBlockN;
+      for (int kb = 0; kb < nkb; ++kb) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[s]), ph, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t sa = stage_base + s * kStageBytes;
+        const uint32_t sb = sa + kATileBytes;
+        if (MODE == kTN) {
+          // Last k-block of an expert: contraction rows past the expert's end
+          // belong to the next expert (or are TMA zero fill).  Zero them in both
+          // operands so they add nothing, then make the writes visible to the
+          // tensor core's (async-proxy) reads.
+          const int rem = t.k_len - kb * kBlockK;
+          if (rem < kBlockK) {
+            const uint32_t skip = rem * 128u;
+            const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+            for (uint32_t box = 0; box < kStageBytes / kBoxBytes; ++box) {
+              uint8_t* bp = smem + size_t(s) * kStageBytes + box * kBoxBytes;
+              for (uint32_t off = skip + lane * 16u; off < kBoxBytes; off += 512u)
+                *reinterpret_cast<uint4*>(bp + off) = zero;
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+          }
+        }
+        if (lane == 0) {
+          // K-major SW128 operand: 8-row groups 1024 B apart, +32 B per 16-wide k step.
+          // MN-major SW128 operand: 64-wide boxes 8 KiB apart (LBO), 8-k-row groups
+          // 1024 B apart (SBO), +2048 B per 16-deep k step.
+          const uint64_t adesc = kAMn ? ptx::make_smem_desc(sa, kBoxBytes, 1024u)
+                                      : ptx::make_smem_desc(sa, 16u, 1024u);
+          const uint64_t bdesc = kBMn ? ptx::make_smem_desc(sb, kBoxBytes, 1024u)
+                                      : ptx::make_smem_desc(sb, 16u, 1024u);
+          constexpr uint64_t a_step = kAMn ? (2048u >> 4) : (32u >> 4);
+          constexpr uint64_t b_step = kBMn ? (2048u >> 4) : (32u >> 4);
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k)
+            ptx::mma_bf16_ss(d_tmem, adesc + k * a_step, bdesc + k * b_step, kIdesc,
+                             (kb | k) != 0 ? 1u : 0u);
+          ptx::mma_commit(ptx::smem_u32(&tail->empty[s]));
+        }
+        __syncwarp();
+        if (++s == kStages) { s = 0; ph ^= 1u; }
+      }
+      if (ok && lane == 0) ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[ab]));
+      __syncwarp();
+    }
+  } else {
+    // ---------------------------------------------------------- epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    TileWalker walk(p, tail->row_start, tail->tile_start);
+    Tile t;
+    uint32_t it = 0;
+    bool ok = true;
+    while (ok && walk.next(&t)) {
+      const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+      const int r = q * 32 + lane;
+      const bool row_ok = r < t.valid_rows;
+      const int64_t out_row = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0 + r)
+                                            : (int64_t(t.row0) + r);
+      __nv_bfloat16* crow = c + out_row * p.n + t.col0;
+      const int cols_left = static_cast<int>(p.n) - t.col0;  // multiple of 8
+      if (nkb == 0) {
+        if (row_ok) {
+          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+          for (int col = 0; col < kBlockN && col < cols_left; col += 8)
+            *reinterpret_cast<uint4*>(crow + col) = zero;
+        }
+        continue;
+      }
+      const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
+      ++it;
+      if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[ab]), aph, abort_flag)) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN;
+#pragma unroll 1
+      for (int ch = 0; ch < kBlockN / 32; ++ch) {
+        uint32_t v[32];
+        ptx::tmem_ld_32x32(taddr + ch * 32, v);
+        ptx::tmem_ld_wait();
+        if (row_ok) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int col = ch * 32 + j * 8;
+            if (col < cols_left) {
+              uint4 o;
+              __nv_bfloat162 h;
+              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+              o.x = *reinterpret_cast<uint32_t*>(&h);
+              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+              o.y = *reinterpret_cast<uint32_t*>(&h);
+              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+              o.z = *reinterpret_cast<uint32_t*>(&h);
+              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+              o.w = *reinterpret_cast<uint32_t*>(&h);
+              *reinterpret_cast<uint4*>(crow + col) = o;
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[ab]));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait gave up.  Report it, then give copies and MMAs still in flight time
+    // to land before shared memory and TMEM are handed back.
+    if (threadIdx.x == 0 && status != nullptr) atomicOr(status, 0x1u);
+    const uint64_t t0 = ptx::globaltimer_ns();
+    while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    ptx::tc_fence_after_sync();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// Argument fill on its own (bit-exact tests, inspection): same scan as above,
+// writes the reference's nine per-expert values (schedule.cuh: fill_fields).
+__global__ void __launch_bounds__(32, 1)
+fill_offsets_kernel(const int64_t* __restrict__ batch_sizes, const Problem p, int64_t* __restrict__ out) {
+  const int lane = threadIdx.x;
+  int64_t carry = 0;
+  for (int base = 0; base < p.z; base += 32) {
+    const int e = base + lane;
+    const int64_t v = (e < p.z) ? batch_sizes[e] : 0;
+    int64_t incl = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += up;
+    }
+    if (e < p.z) fill_fields(p, e, carry + incl - v, v, out + int64_t(e) * 9);
+    carry += __shfl_sync(0xffffffffu, incl, 31);
+  }
+}
+
+}  // namespace b200gmm

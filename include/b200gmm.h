@@ -1,0 +1,131 @@
+/*
+ * b200gmm.h — C ABI of the B200 (sm_100a) grouped-GEMM core library.
+ *
+ * Plain pointers and sizes only; no torch types cross this boundary.  All
+ * functions return 0 on success or a negative B200GMM_E* code and never throw.
+ * Work is enqueued on the CUDA stream the caller passes and is asynchronous
+ * with respect to the host; no entry point synchronises the device unless its
+ * comment says so.  Tensors are bf16, contiguous, row-major; batch_sizes is
+ * int64.  The device current at the time of the call must own the pointers.
+ *
+ * Every declaration cites the piece of the reference (tgale96/grouped_gemm,
+ * paths relative to that project) whose job it takes over.
+ */
+#ifndef B200GMM_H_
+#define B200GMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Error codes (b200gmm_strerror gives the text). */
+#define B200GMM_OK 0
+#define B200GMM_EINVAL -1       /* bad argument combination (e.g. both transposes) */
+#define B200GMM_EALIGN -2       /* a row length is not a multiple of 8 elements */
+#define B200GMM_ELIMIT -3       /* too many experts / too many tiles / dim too large */
+#define B200GMM_EWORKSPACE -4   /* workspace missing, too small or misaligned */
+#define B200GMM_ECUDA -5        /* a CUDA runtime or driver call failed */
+#define B200GMM_ETENSORMAP -6   /* cuTensorMapEncodeTiled rejected a tensor */
+#define B200GMM_EDEVICE -7      /* not an sm_100 device */
+#define B200GMM_ETIMEOUT -8     /* (status word) a bounded wait inside the kernel gave up */
+
+/* Largest number of experts one call accepts.  The reference caps the
+ * device-side path at 512 (csrc/fill_arguments.cuh:11, csrc/grouped_gemm.cu:120-124). */
+#define B200GMM_MAX_EXPERTS 1024
+
+/* Bits of the device status word written by the kernels (0 = clean run). */
+#define B200GMM_STATUS_TIMEOUT 0x1u        /* a bounded mbarrier wait ran out */
+#define B200GMM_STATUS_NEGATIVE_SIZE 0x2u  /* a batch size was < 0 (treated as 0) */
+#define B200GMM_STATUS_ROWS_OVERFLOW 0x4u  /* sum(batch_sizes) > rows of a (clamped) */
+
+/* Number of int64 fields b200gmm_fill_offsets writes per expert:
+ * m, n, k, lda, ldb, ldc, a_offset, b_offset, c_offset (offsets in elements). */
+#define B200GMM_FILL_FIELDS 9
+
+/*
+ * Bytes of device scratch b200gmm_run needs for `z` experts.  The scratch holds
+ * a device copy of batch_sizes (when the caller's copy is in host memory) and
+ * the status word.  Replaces the seven per-call torch::empty scratch tensors of
+ * csrc/grouped_gemm.cu:119-138 (MakeArgumentsOnDevice) and the seven H2D copies
+ * of csrc/grouped_gemm.cu:83-94, :209-218 (CopyToDevice).
+ */
+int b200gmm_workspace_bytes(int z, size_t* out_bytes);
+
+/*
+ * The grouped GEMM itself: one persistent kernel launch for all experts.
+ * Replaces grouped_gemm::GroupedGemm (csrc/grouped_gemm.cu:470-564, prototype
+ * csrc/grouped_gemm.h:5-9) together with the argument fill
+ * (csrc/fill_arguments.cuh:34-131) that precedes the CUTLASS launch.
+ *
+ *   trans_a=0, trans_b=0:  c[rows_i, :] = a[rows_i, :] @ b[i]        a[T,k] b[z,k,n] c[T,n]
+ *   trans_a=0, trans_b=1:  c[rows_i, :] = a[rows_i, :] @ b[i]^T      a[T,k] b[z,n,k] c[T,n]
+ *   trans_a=1, trans_b=0:  c[i] = a[rows_i, :]^T @ b[rows_i, :]      a[T,m] b[T,n]   c[z,m,n]
+ *
+ * rows_i is the i-th run of batch_sizes[i] consecutive rows.  `dim_a1` is
+ * a's second dimension (k, or m when trans_a), `n` the output's last
+ * dimension.  For trans_a every c[i] is written, as zeros when
+ * batch_sizes[i]==0 (csrc/fill_arguments.cuh:100-119).  Rows of c past
+ * sum(batch_sizes) are left untouched, as in the reference.
+ *
+ * batch_sizes may live in host memory (batch_sizes_on_device=0: it is copied
+ * into the workspace with one cudaMemcpyAsync, so the host array must stay
+ * valid until that copy has been issued, i.e. until this call returns when the
+ * host array is pageable) or in device memory (=1: never read by the host, no
+ * synchronisation).
+ *
+ * `workspace` is device memory of at least b200gmm_workspace_bytes(z) bytes,
+ * 16-byte aligned, owned by the caller and reusable once the stream has passed
+ * this call.  If `device_status` is non-NULL it must point to a 4-byte device
+ * word that the kernel ORs B200GMM_STATUS_* bits into (the caller clears it).
+ */
+int b200gmm_run(const void* a, const void* b, void* c,
+                const int64_t* batch_sizes, int batch_sizes_on_device,
+                int z, int64_t tokens, int64_t dim_a1, int64_t n,
+                int trans_a, int trans_b,
+                void* workspace, size_t workspace_bytes,
+                uint32_t* device_status, void* cuda_stream);
+
+/*
+ * Device-side argument fill on its own, for inspection and bit-exact tests:
+ * runs the same warp-scan the GEMM kernel runs in its prologue and writes
+ * z x B200GMM_FILL_FIELDS int64 values (expert-major) to `out_device`.
+ * Semantics of each field follow FillArguments (csrc/fill_arguments.cuh:59-78)
+ * and its host twin MakeArgumentsOnHost (csrc/grouped_gemm.cu:160-175),
+ * evaluated in int64.  `batch_sizes_device` must be device memory.
+ */
+int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z,
+                         int64_t dim_a1, int64_t n, int trans_a, int trans_b,
+                         int64_t* out_device, void* cuda_stream);
+
+/*
+ * Host replay of the tile schedule the persistent kernel walks (same
+ * __host__ __device__ code as the kernel).  Writes, for every tile index in
+ * launch order, {expert, row0, col0, valid_rows, k_blocks} as int64 into `out`
+ * (5 per tile, at most `max_tiles` tiles) and the tile count into *n_tiles.
+ * Pure host arithmetic; needs no GPU.  It has no counterpart in the reference,
+ * whose schedule lives inside CUTLASS (GroupScheduleMode::kDeviceOnly,
+ * csrc/grouped_gemm.cu:256-259).
+ */
+int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z,
+                          int64_t tokens, int64_t dim_a1, int64_t n,
+                          int trans_a, int trans_b,
+                          int64_t* out, int64_t max_tiles, int64_t* n_tiles);
+
+/* Tile shape the kernels use: out[0]=rows, out[1]=cols, out[2]=k depth. */
+int b200gmm_tile_shape(int trans_a, int trans_b, int* out3);
+
+/* Number of kernels this library has launched in this process (all entry
+ * points), for launch accounting in benchmarks. */
+int64_t b200gmm_launch_count(void);
+
+/* Text for an error code.  Replaces the TORCH_CHECK messages of
+ * csrc/grouped_gemm.cu:21-32. */
+const char* b200gmm_strerror(int code);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GMM_H_ */
