@@ -1,0 +1,553 @@
+#!/usr/bin/env python
+"""Benchmark of the grouped-GEMM hot path on B200.
+
+    python bench.py --gpus 1 --steps K --warmup W            # this library
+    python bench.py --impl reference --steps K --warmup W    # CPU per-expert loop
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+One JSON line on stdout (rank 0).  Workloads (synthetic, seeded; bf16):
+
+* N = 1: Mixtral-8x7B expert up-projection, z=8, 32768 rows (16384 tokens x
+  top-2), k=4096, n=14336, batch sizes multinomial(Dirichlet(1), seed 1).  A step
+  is forward (a@b) + dgrad (grad@b^T) + wgrad (a^T@grad): three kernel launches.
+* N > 1: expert-parallel projection, z=64 experts sharded evenly, 65536 tokens x
+  top-4 = 262144 rows, hidden 6144, ffn 10752, uniform routing seed 3.  A step is
+  dispatch (all-to-all) -> forward -> combine, then dispatch of the output
+  gradient -> dgrad + wgrad -> combine.  Total work is fixed ("strong" scaling).
+
+``value`` is TFLOP/s over the timed steps with inputs resident in HBM, timed with
+CUDA events (max over ranks).  ``e2e`` is the same step driven from pinned host
+buffers with the host<->device copies inside the timed region.
+"""
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "gmm bf16 throughput, fwd+dgrad+wgrad"
+UNIT = "TFLOP/s"
+
+
+# ----------------------------------------------------------------------------- workloads
+def mixtral_batch_sizes():
+    """BASELINE config 2: multinomial(32768, Dirichlet(alpha=1)), seed 1."""
+    rng = np.random.default_rng(1)
+    p = rng.dirichlet(np.ones(8))
+    return [int(v) for v in rng.multinomial(32768, p)]
+
+
+def fine_grained_batch_sizes():
+    """BASELINE config 4: 256 experts, Zipf(1.1) popularity, 51 forced empty, 65536 rows, seed 2."""
+    rng = np.random.default_rng(2)
+    perm = rng.permutation(256)
+    w = np.zeros(256)
+    w[perm] = 1.0 / np.arange(1, 257) ** 1.1
+    zero = rng.choice(256, 51, replace=False)
+    w[zero] = 0
+    w /= w.sum()
+    return [int(v) for v in rng.multinomial(65536, w)]
+
+
+def ep_routing(tokens=65536, experts=64, top_k=4):
+    """BASELINE config 5: uniform-random top-k distinct experts per token, seed 3."""
+    rng = np.random.default_rng(3)
+    idx = np.argsort(rng.random((tokens, experts)), axis=1)[:, :top_k]
+    return torch.from_numpy(np.ascontiguousarray(idx)).to(torch.int64)
+
+
+MIXTRAL = dict(z=8, rows=32768, k=4096, n=14336)
+EP = dict(z=64, tokens=65536, top_k=4, hidden=6144, ffn=10752)
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while a region runs.
+    Read-only: never sets a clock or any other device state."""
+
+    REASONS = {
+        0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+        0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
+    }
+
+    def __init__(self, index, period=0.05):
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = index
+            if visible:
+                ids = [v for v in visible.split(",") if v.strip() != ""]
+                if index < len(ids) and ids[index].strip().isdigit():
+                    phys = int(ids[index])
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ----------------------------------------------------------------------------- helpers
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"source": "measured", "hbm_gbs": p["hbm_gbs"], "burst": p["bf16_tflops"],
+                "sustained": p.get("bf16_tflops_sustained", p["bf16_tflops"])}
+    return {"source": "fallback", "hbm_gbs": 6650.0, "burst": 1590.0, "sustained": 1400.0}
+
+
+def dist_info():
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return world, rank, local
+
+
+def timed_region(fn, steps, world):
+    """Barrier + synchronize, K steps between two CUDA events on the current
+    stream, synchronize + barrier; returns the max-over-ranks milliseconds."""
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        dist.barrier()
+    return float(ms.item())
+
+
+# ----------------------------------------------------------------------------- CPU baseline
+def cpu_sample_inputs(frac):
+    """The Mixtral workload with each expert's rows cut to ``frac`` of its size
+    (full k and n, full weights)."""
+    sizes = [max(1, int(s * frac)) for s in mixtral_batch_sizes()]
+    rows = sum(sizes)
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(rows, MIXTRAL["k"], generator=g).bfloat16()
+    b = (torch.randn(MIXTRAL["z"], MIXTRAL["k"], MIXTRAL["n"], generator=g) * 0.02).bfloat16()
+    grad = torch.randn(rows, MIXTRAL["n"], generator=g).bfloat16()
+    return sizes, a, b, grad
+
+
+def cpu_step(sizes, a, b, grad):
+    """Reference CPU path: the per-expert torch.matmul loop of the reference's
+    tests, forward + dgrad + wgrad."""
+    from oracle import gmm_oracle
+    bs = torch.tensor(sizes)
+    gmm_oracle.torch_loop_bf16(a, b, bs, trans_b=False)
+    gmm_oracle.torch_loop_bf16(grad, b, bs, trans_b=True)
+    gmm_oracle.torch_loop_tn_bf16(a, grad, bs)
+    return 3 * 2.0 * sum(sizes) * MIXTRAL["k"] * MIXTRAL["n"]
+
+
+def calibrate_cpu(target_s):
+    """Pick the row fraction whose step takes about ``target_s`` seconds."""
+    frac = 1.0 / 256
+    sizes, a, b, grad = cpu_sample_inputs(frac)
+    cpu_step(sizes, a, b, grad)  # warm-up (thread pool, oneDNN primitives)
+    t0 = time.perf_counter()
+    flops = cpu_step(sizes, a, b, grad)
+    dt = max(time.perf_counter() - t0, 1e-4)
+    rate = flops / dt
+    full = 3 * 2.0 * MIXTRAL["rows"] * MIXTRAL["k"] * MIXTRAL["n"]
+    return min(1.0, max(1.0 / 256, target_s * rate / full))
+
+
+def cpu_baseline(target_s=12.0):
+    frac = calibrate_cpu(target_s)
+    sizes, a, b, grad = cpu_sample_inputs(frac)
+    cpu_step(sizes, a, b, grad)
+    t0 = time.perf_counter()
+    flops = cpu_step(sizes, a, b, grad)
+    dt = time.perf_counter() - t0
+    return {
+        "value": flops / dt / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
+        "host_cpus": os.cpu_count(), "kind": "port",
+        "sample": f"per-expert torch.matmul loop (bf16, CPU) on {sum(sizes)} of {MIXTRAL['rows']} rows "
+                  f"(each expert cut to {frac:.4f} of its rows), full k/n/weights, fwd+dgrad+wgrad, "
+                  f"one pass of {dt:.1f} s",
+    }
+
+
+def run_reference(args):
+    """--impl reference: the reference's CPU-runnable path (its test oracle's
+    per-expert matmul loop; the CUDA extension itself cannot be built without
+    the CUTLASS submodule and has no CPU code) on this box's host cores."""
+    world, rank, _ = dist_info()
+    if rank != 0:
+        return
+    frac = calibrate_cpu(3.0)
+    sizes, a, b, grad = cpu_sample_inputs(frac)
+    for _ in range(args.warmup):
+        cpu_step(sizes, a, b, grad)
+    t0 = time.perf_counter()
+    flops = 0.0
+    for _ in range(args.steps):
+        flops += cpu_step(sizes, a, b, grad)
+    dt = time.perf_counter() - t0
+    value = flops / dt / 1e12
+    sample = (f"per-expert torch.matmul loop (bf16, CPU) on {sum(sizes)} of {MIXTRAL['rows']} rows per step "
+              f"(each expert cut to {frac:.4f} of its rows), full k/n/weights")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
+                         "host_cpus": os.cpu_count(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------- our arm
+def workload_config(n_gpus):
+    if n_gpus == 1:
+        return {"workload": "mixtral-8x7b expert up-projection fwd+dgrad+wgrad (BASELINE configs[2] on "
+                            "configs[1] shapes): z=8 rows=32768 k=4096 n=14336, batch_sizes "
+                            "multinomial(Dirichlet(1), seed 1), on device",
+                "batch_sizes": mixtral_batch_sizes(),
+                "l2": "inputs larger than L2 (2.1 GB read per pass, no flush)"}
+    return {"workload": f"expert-parallel projection fwd+dgrad+wgrad (BASELINE configs[4]): z=64 sharded over "
+                        f"{n_gpus} ranks, 65536 tokens x top-4 = 262144 rows, hidden 6144, ffn 10752, uniform "
+                        "routing seed 3, NCCL all-to-all dispatch/combine",
+            "parallelism": f"ep{n_gpus}",
+            "l2": "inputs larger than L2 (per-rank operands of several GB, no flush)"}
+
+
+def time_loop(fn, iters):
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def run_single(args):
+    from grouped_gemm_b200 import _capi, backend
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["k"], MIXTRAL["n"]
+    sizes = mixtral_batch_sizes()
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+    b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    grad = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device=dev)
+    flops_pass = 2.0 * rows * k * n
+
+    def fwd():
+        return backend.gmm(a, b, bs)
+
+    def dgrad():
+        return backend.gmm(grad, b, bs, trans_b=True)
+
+    def wgrad():
+        return backend.gmm(a, grad, bs, trans_a=True)
+
+    def step():
+        fwd(); dgrad(); wgrad()
+
+    for _ in range(args.warmup):
+        step()
+    launches0 = _capi.launch_count()
+    with ClockSampler(0) as clocks:
+        ms_total = timed_region(step, args.steps, 1)
+    launches = _capi.launch_count() - launches0
+    ms_step = ms_total / args.steps
+    value = 3 * flops_pass / ms_step / 1e9
+
+    # per-pass device times (each loop alone; the dominant kernel's figure feeds the roofline)
+    iters = max(args.steps, 5)
+    passes = {}
+    for name, fn in (("fwd", fwd), ("dgrad", dgrad), ("wgrad", wgrad)):
+        fn()
+        ms = time_loop(fn, iters)
+        passes[name] = {"ms": ms, "tflops": flops_pass / ms / 1e9}
+    peaks = measured_peaks()
+    top = max(passes, key=lambda p: passes[p]["ms"])
+    kernel_of = {"fwd": "gmm_kernel<NN>", "dgrad": "gmm_kernel<NT>", "wgrad": "gmm_kernel<TN>"}
+    roofline = {
+        "bound": "tensor", "kernel": kernel_of[top], "achieved": passes[top]["tflops"],
+        "peak": peaks["burst"], "unit": "TFLOP/s", "frac": passes[top]["tflops"] / peaks["burst"],
+        "peak_source": f"{peaks['source']} cuBLAS bf16 burst (kernel timed alone)",
+        "step_frac_of_sustained": value / peaks["sustained"],
+        "flops_per_launch": flops_pass, "ms_per_launch": passes[top]["ms"],
+        "traffic": TRAFFIC_BYTES.get(kernel_of[top]),
+        "algorithmic_bytes": 2.0 * (rows * k + z * k * n + rows * n),
+    }
+
+    # small-M, HBM-bound group shapes (BASELINE config 4, forward): report GB/s
+    hbm = fine_grained_hbm(backend, dev, peaks)
+
+    # end to end: pinned host buffers in and out, copies inside the timed region
+    e2e = e2e_single(backend, a, b, grad, bs, flops_pass, min(args.steps, 3))
+
+    scaling_base = ep_value_single(args) if args.scaling_base else None
+    baseline = cpu_baseline() if not args.no_cpu_baseline else None
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(1),
+        "passes": passes, "roofline": roofline, "hbm_bound_case": hbm, "cpu_baseline": baseline,
+        "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
+        "frac_of_nominal_2250": value / 2250.0, "device_status": backend.device_status(),
+    }
+    if scaling_base is not None:
+        line["scaling_base"] = scaling_base
+    print(json.dumps(line), flush=True)
+
+
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch at the
+# benchmark's size, from the ncu captures summarised under profiles/.
+TRAFFIC_BYTES = {}
+
+
+def fine_grained_hbm(backend, dev, peaks):
+    """Forward of BASELINE config 4 (z=256, k=7168, n=2048, 65536 rows, ~20 %
+    empty experts): most groups have < 128 rows, so the weights dominate the
+    traffic and the HBM roofline is the bound.  Algorithmic bytes: a + weights of
+    non-empty experts + c."""
+    sizes = fine_grained_batch_sizes()
+    z, k, n, rows = 256, 7168, 2048, 65536
+    g = torch.Generator(device=dev).manual_seed(2)
+    a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+    b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device=dev)
+    fn = lambda: backend.gmm(a, b, bs)
+    for _ in range(3):
+        fn()
+    ms = time_loop(fn, 10)
+    nonempty = sum(1 for s in sizes if s > 0)
+    nbytes = 2.0 * (rows * k + nonempty * k * n + rows * n)
+    flops = 2.0 * rows * k * n
+    return {"workload": "config 4 forward: z=256 k=7168 n=2048 rows=65536, 51 empty experts, median 59 rows",
+            "ms": ms, "gbs": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
+            "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes}
+
+
+def e2e_single(backend, a, b, grad, bs, flops_pass, steps):
+    dev = a.device
+    host_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in (a, b, grad)]
+    da, db, dg = (torch.empty_like(t) for t in (a, b, grad))
+    outs_shape = [(a.shape[0], b.shape[2]), (a.shape[0], a.shape[1]), tuple(b.shape)]
+    host_out = [torch.empty(s, dtype=torch.bfloat16, pin_memory=True) for s in outs_shape]
+    h2d = sum(t.numel() * 2 for t in host_in)
+    d2h = sum(t.numel() * 2 for t in host_out)
+
+    def step():
+        da.copy_(host_in[0], non_blocking=True)
+        db.copy_(host_in[1], non_blocking=True)
+        dg.copy_(host_in[2], non_blocking=True)
+        c = backend.gmm(da, db, bs)
+        dx = backend.gmm(dg, db, bs, trans_b=True)
+        dw = backend.gmm(da, dg, bs, trans_a=True)
+        host_out[0].copy_(c, non_blocking=True)
+        host_out[1].copy_(dx, non_blocking=True)
+        host_out[2].copy_(dw, non_blocking=True)
+
+    step()
+    ms = timed_region(step, steps, 1) / steps
+    return {"value": 3 * flops_pass / ms / 1e9, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "what": "pinned host a, b, grad -> device; fwd+dgrad+wgrad through grouped_gemm_b200.backend.gmm; "
+                    "c, dgrad, wgrad -> pinned host"}
+
+
+def ep_setup(world, rank, dev):
+    from grouped_gemm_b200 import expert_parallel as ep
+    ids = ep_routing(EP["tokens"], EP["z"], EP["top_k"])
+    per = EP["tokens"] // world
+    local_ids = ids[rank * per:(rank + 1) * per].to(dev)
+    plan = ep.build_plan(local_ids, EP["z"])
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    x = torch.randn(per, EP["hidden"], device=dev, generator=g).bfloat16()
+    w = (torch.randn(EP["z"] // world, EP["hidden"], EP["ffn"], device=dev, generator=g) * 0.02).bfloat16()
+    grad = torch.randn(per * EP["top_k"], EP["ffn"], device=dev, generator=g).bfloat16()
+    return ep, plan, x, w, grad
+
+
+def ep_flops():
+    return 3 * 2.0 * EP["tokens"] * EP["top_k"] * EP["hidden"] * EP["ffn"]
+
+
+def ep_value_single(args):
+    """Config 5 on one GPU (all 64 experts local, no exchange): the denominator
+    for strong-scaling efficiency of the multi-GPU lines."""
+    from grouped_gemm_b200 import backend
+    dev = torch.device("cuda", 0)
+    ep, plan, x, w, grad = ep_setup(1, 0, dev)
+    gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
+    step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+    for _ in range(2):
+        step()
+    steps = max(2, min(args.steps, 5))
+    ms = timed_region(step, steps, 1) / steps
+    out = {"workload": workload_config(2)["workload"].replace("over 2 ranks", "over 1 rank"),
+           "value": ep_flops() / ms / 1e9, "unit": UNIT, "ms_per_step": ms, "steps": steps}
+    del x, w, grad, plan
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_multi(args):
+    import torch.distributed as dist
+    from grouped_gemm_b200 import _capi, backend
+    world, rank, local = dist_info()
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    ep, plan, x, w, grad = ep_setup(world, rank, dev)
+    gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
+    step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    launches0 = _capi.launch_count()
+    with ClockSampler(local) as clocks:
+        ms_total = timed_region(step, args.steps, world)
+    launches = (_capi.launch_count() - launches0) * world
+    ms_step = ms_total / args.steps
+    value = ep_flops() / ms_step / 1e9
+
+    # split: local GEMMs alone (max over ranks), to show the exchange share
+    a = ep.dispatch(x, plan)
+    gl = ep.dispatch_rows(grad, plan)
+
+    def gemms():
+        backend.gmm(a, w, plan.batch_sizes)
+        backend.gmm(gl, w, plan.batch_sizes, trans_b=True)
+        backend.gmm(a, gl, plan.batch_sizes, trans_a=True)
+
+    gemms()
+    ms_gemm = timed_region(gemms, args.steps, world) / args.steps
+    del a, gl
+
+    # end to end from pinned host buffers
+    hx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True).copy_(x)
+    hg = torch.empty(grad.shape, dtype=grad.dtype, pin_memory=True).copy_(grad)
+    ho = torch.empty(grad.shape, dtype=grad.dtype, pin_memory=True)
+    hdx = torch.empty(x.shape, dtype=x.dtype, pin_memory=True)
+    hdw = torch.empty(w.shape, dtype=w.dtype, pin_memory=True)
+
+    def e2e_step():
+        x.copy_(hx, non_blocking=True)
+        grad.copy_(hg, non_blocking=True)
+        out_rows, dx, dw = ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+        ho.copy_(out_rows, non_blocking=True)
+        hdx.copy_(dx, non_blocking=True)
+        hdw.copy_(dw, non_blocking=True)
+
+    e2e_step()
+    e2e_steps = min(args.steps, 3)
+    ms_e2e = timed_region(e2e_step, e2e_steps, world) / e2e_steps
+    peaks = measured_peaks()
+    status = torch.tensor([backend.device_status(dev)], device=dev)
+    dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(world),
+            "roofline": {"bound": "tensor", "kernel": "gmm_kernel<NN|NT|TN> (local GEMMs of one step)",
+                         "achieved": ep_flops() / world / ms_gemm / 1e9, "peak": peaks["sustained"],
+                         "unit": "TFLOP/s", "frac": ep_flops() / world / ms_gemm / 1e9 / peaks["sustained"],
+                         "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (per GPU)", "traffic": None},
+            "exchange_share": 1.0 - ms_gemm / ms_step, "ms_gemm_per_step": ms_gemm,
+            "cpu_baseline": None,
+            "e2e": {"value": ep_flops() / ms_e2e / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
+                    "h2d_bytes_per_step": (hx.numel() + hg.numel()) * 2 * world,
+                    "d2h_bytes_per_step": (ho.numel() + hdx.numel() + hdw.numel()) * 2 * world},
+            "gpu_launches": launches, "clocks": clocks.summary(), "device_status": int(status.item()),
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--scaling-base", action="store_true",
+                    help="also time the multi-GPU workload on this one GPU (strong-scaling denominator)")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+    world, _, _ = dist_info()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path "
+                         "(use --impl reference for the CPU baseline)")
+    if world > 1 or args.gpus > 1:
+        if world != args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+        return run_multi(args)
+    return run_single(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,62 @@
+"""CPU-only checks of the Python mirror of the reference API: names, argument
+checks and error types (no kernel runs; every case fails validation first)."""
+import inspect
+
+import pytest
+import torch
+
+import grouped_gemm_b200 as grouped_gemm
+from grouped_gemm_b200 import backend, ops
+
+
+def test_api_surface_matches_reference():
+    # grouped_gemm/__init__.py:1-2, ops.py:32-33, backend.py:24
+    assert grouped_gemm.ops is ops and grouped_gemm.backend is backend
+    assert list(inspect.signature(ops.gmm).parameters) == ["a", "b", "batch_sizes", "trans_b"]
+    assert list(inspect.signature(backend.gmm).parameters) == [
+        "a", "b", "batch_sizes", "trans_a", "trans_b", "c"]
+    assert issubclass(ops.GroupedGemm, torch.autograd.Function)
+    # the test-suite of the reference reaches the backend through ops (ops_test.py:154)
+    assert ops.backend.gmm is backend.gmm
+    assert list(inspect.signature(backend.backend.gmm).parameters) == [
+        "a", "b", "c", "batch_sizes", "trans_a", "trans_b"]
+
+
+def _t(*shape, dtype=torch.bfloat16):
+    return torch.zeros(*shape, dtype=dtype)
+
+
+def test_allocate_output_shapes_and_asserts():
+    bs = torch.tensor([4, 4])
+    assert backend._allocate_output(_t(8, 16), _t(2, 16, 24), bs, False, False).shape == (8, 24)
+    assert backend._allocate_output(_t(8, 16), _t(2, 24, 16), bs, False, True).shape == (8, 24)
+    assert backend._allocate_output(_t(8, 16), _t(8, 24), bs, True, False).shape == (2, 16, 24)
+    with pytest.raises(AssertionError):
+        backend._allocate_output(_t(8, 16), _t(2, 16, 24), bs, True, True)
+    with pytest.raises(AssertionError):
+        backend._allocate_output(_t(8, 16), _t(2, 16, 24), bs.view(1, 2), False, False)
+    with pytest.raises(AssertionError):
+        backend._allocate_output(_t(2, 4, 16), _t(2, 16, 24), bs, False, False)
+    with pytest.raises(AssertionError):
+        backend._allocate_output(_t(8, 16), _t(16, 24), bs, False, False)
+
+
+@pytest.mark.parametrize("kwargs,fragment", [
+    (dict(trans_a=True, trans_b=True), "only one of"),
+    (dict(batch_sizes=torch.tensor([4, 4], dtype=torch.int32)), "int64"),
+    (dict(batch_sizes=torch.tensor([[4, 4]])), "1-D"),
+    (dict(), "a must be a CUDA tensor"),
+])
+def test_native_binding_checks_raise_runtime_error(kwargs, fragment):
+    args = dict(a=_t(8, 16), b=_t(2, 16, 24), c=_t(8, 24), batch_sizes=torch.tensor([4, 4]),
+                trans_a=False, trans_b=False)
+    args.update(kwargs)
+    with pytest.raises(RuntimeError, match=fragment):
+        backend.backend.gmm(args["a"], args["b"], args["c"], args["batch_sizes"], args["trans_a"],
+                            args["trans_b"])
+
+
+def test_no_cpu_fallback():
+    """CPU tensors are refused, not computed some other way."""
+    with pytest.raises(RuntimeError):
+        ops.gmm(_t(8, 16), _t(2, 16, 24), torch.tensor([4, 4]))

@@ -1,0 +1,297 @@
+"""GPU parity tests (run with -m gpu on a B200).  Every product goes through the
+C ABI (grouped_gemm_b200.backend -> b200gmm_run); the CPU oracle is the checker.
+
+Tolerance for floating-point results: rtol 1e-2 / atol 1e-2 in bf16 against the
+fp32-accumulated oracle.  Integer results (argument fill) are compared exactly.
+The reference's own statistic (<= 2 % of elements outside isclose(rtol=1e-5),
+grouped_gemm/ops_test.py:10-17) is checked as well on its test grid.
+"""
+import itertools
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import gmm_oracle
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gg():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    import grouped_gemm_b200
+    return grouped_gemm_b200
+
+
+@pytest.fixture(autouse=True)
+def _clean_status(gg):
+    yield
+    assert gg.backend.device_status() == 0, "a kernel raised a status bit (timeout / bad sizes)"
+
+
+def _check_fwd_bwd(gg, a_cpu, b_cpu, bs_cpu, trans_b, on_device, ref_stat=True):
+    """Forward + out.sum().backward() as in ops_test.py:59-80, against the oracle."""
+    a = a_cpu.cuda().requires_grad_(True)
+    b = b_cpu.cuda().requires_grad_(True)
+    bs = bs_cpu.cuda() if on_device else bs_cpu
+    out = gg.ops.gmm(a, b, bs, trans_b)
+    want = gmm_oracle.gmm(a_cpu, b_cpu, bs_cpu, trans_b=trans_b)
+    rows = int(bs_cpu.sum())
+    util.assert_close(out[:rows], want[:rows], what="forward")
+    out.sum().backward()
+    agrad, bgrad = gmm_oracle.gmm_backward(a_cpu, b_cpu, bs_cpu, torch.ones_like(want), trans_b=trans_b)
+    util.assert_close(a.grad[:rows], agrad[:rows], what="a.grad")
+    util.assert_close(b.grad, bgrad, what="b.grad")
+    if ref_stat:
+        assert gmm_oracle.reference_allclose_pct(out[:rows].cpu(), want[:rows]) <= 2.0
+        assert gmm_oracle.reference_allclose_pct(a.grad[:rows].cpu(), agrad[:rows]) <= 2.0
+        assert gmm_oracle.reference_allclose_pct(b.grad.cpu(), bgrad) <= 2.0
+
+
+# ---- the reference's grid: ops_test.py:20-36 ---------------------------------
+_PROBLEMS = [(1, 128, 128, 128), (8, 128, 128, 128), (16, 128, 128, 128),
+             (1, 128, 256, 512), (8, 128, 256, 512), (16, 128, 256, 512)]
+_GRID = [p + f for p, f in itertools.product(_PROBLEMS, itertools.product((False, True), (False, True)))]
+
+
+@pytest.mark.parametrize("z,m,k,n,trans_b,on_device", _GRID)
+def test_fixed_sizes(gg, z, m, k, n, trans_b, on_device):
+    torch.manual_seed(0)
+    a = util.reference_inputs(z, m, k).view(-1, k)
+    b = util.reference_inputs(z, n, k) if trans_b else util.reference_inputs(z, k, n)
+    _check_fwd_bwd(gg, a, b, torch.tensor([m] * z), trans_b, on_device)
+
+
+@pytest.mark.parametrize("z,m,k,n,trans_b,on_device", _GRID)
+def test_variable_sizes(gg, z, m, k, n, trans_b, on_device):
+    torch.manual_seed(0)
+    a = util.reference_inputs(z, m, k).view(-1, k)
+    b = util.reference_inputs(z, n, k) if trans_b else util.reference_inputs(z, k, n)
+    _check_fwd_bwd(gg, a, b, util.variable_batch_sizes(z, m), trans_b, on_device)
+
+
+# ---- edge cases: ops_test.py:112-158 -------------------------------------------
+@pytest.mark.parametrize("on_device", [False, True])
+def test_zero_k_known_answer(gg, on_device):
+    a = torch.ones(192, 128).cuda().to(torch.bfloat16)
+    b = torch.ones(192, 128).cuda().to(torch.bfloat16)
+    c = torch.ones(4, 128, 128).cuda().to(torch.bfloat16)
+    bs = torch.tensor([0, 128, 0, 64]).to(torch.long)
+    if on_device:
+        bs = bs.cuda()
+    got = gg.ops.backend.gmm(a, b, bs, trans_a=True, c=c)
+    assert got is c
+    for i, want in enumerate((0, 128, 0, 64)):
+        assert bool((c[i] == want).all()), f"c[{i}] != {want}"
+
+
+@pytest.mark.parametrize("on_device", [False, True])
+def test_zero_size_expert_mixtral_shape(gg, on_device):
+    """ops_test.py:115-141 at a quarter of its width to keep the CPU oracle to
+    seconds; the full Mixtral shape is covered by test_full_size_* below."""
+    torch.manual_seed(0)
+    z, m, k, n = 8, 16384, 1024, 3584
+    a = util.reference_inputs(z, m // z, k).view(-1, k)
+    b = util.reference_inputs(z, k, n)
+    bs = torch.tensor([219, 2246, 5, 8103, 1, 1117, 4693, 0]).to(torch.long)
+    _check_fwd_bwd(gg, a, b, bs, False, on_device)
+
+
+# ---- golden vectors made by the reference's own test functions --------------------
+_DATA, _KEYS = util.golden_cases()
+
+
+@pytest.mark.parametrize("key", _KEYS)
+def test_against_reference_golden(gg, key):
+    z, m, k, n, trans_b, variable = util.parse_key(key)
+    torch.manual_seed(0)
+    a_cpu = util.reference_inputs(z, m, k).view(-1, k)
+    b_cpu = util.reference_inputs(z, n, k) if trans_b else util.reference_inputs(z, k, n)
+    assert util.input_digest(a_cpu, b_cpu) == bytes(_DATA[key + "/input_sha256"]).decode()
+    bs = torch.from_numpy(_DATA[key + "/batch_sizes"])
+    a = a_cpu.cuda().requires_grad_(True)
+    b = b_cpu.cuda().requires_grad_(True)
+    out = gg.ops.gmm(a, b, bs.cuda(), trans_b)
+    out.sum().backward()
+    for got, name in ((out, "out"), (a.grad, "a_grad"), (b.grad, "b_grad")):
+        gold = util.from_bits(_DATA[key + "/" + name])
+        assert gmm_oracle.reference_allclose_pct(got.cpu(), gold) <= 2.0, name
+        util.assert_close(got, gold, rtol=1e-2, atol=1e-6, what=name)
+
+
+# ---- BASELINE config 1 -----------------------------------------------------------
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("on_device", [False, True])
+def test_config1_cpu_correctness_case(gg, trans_b, on_device):
+    torch.manual_seed(0)
+    a_cpu = torch.randn(512, 128).bfloat16()
+    b_cpu = (torch.randn(4, 128, 128) * 0.02).bfloat16()
+    bs = torch.tensor([128] * 4)
+    _check_fwd_bwd(gg, a_cpu, b_cpu, bs, trans_b, on_device, ref_stat=False)
+    # random upstream gradient as well
+    grad_cpu = torch.randn(512, 128).bfloat16()
+    a = a_cpu.cuda().requires_grad_(True)
+    b = b_cpu.cuda().requires_grad_(True)
+    gg.ops.gmm(a, b, bs.cuda() if on_device else bs, trans_b).backward(grad_cpu.cuda())
+    agrad, bgrad = gmm_oracle.gmm_backward(a_cpu, b_cpu, bs, grad_cpu, trans_b=trans_b)
+    util.assert_close(a.grad, agrad, what="a.grad")
+    util.assert_close(b.grad, bgrad, what="b.grad")
+
+
+# ---- ragged / odd shapes, all three layouts ------------------------------------------
+_RAGGED = [
+    ([5, 0, 300, 131], 512, 384),
+    ([77, 129, 1], 200, 328),          # k, n not multiples of the tile
+    ([0, 0, 0], 128, 256),             # nothing to do (wgrad still writes zeros)
+    ([1], 8, 8),                       # smallest legal dims
+    ([64, 64, 63, 65, 127, 129, 128, 0, 256, 257], 256, 520),
+    ([33] * 40, 136, 264),
+]
+
+
+@pytest.mark.parametrize("sizes,d1,n", _RAGGED)
+@pytest.mark.parametrize("mode", ["nn", "nt", "tn"])
+@pytest.mark.parametrize("on_device", [False, True])
+def test_ragged_all_layouts(gg, sizes, d1, n, mode, on_device):
+    torch.manual_seed(1)
+    z, T = len(sizes), sum(sizes)
+    bs_cpu = torch.tensor(sizes, dtype=torch.int64)
+    bs = bs_cpu.cuda() if on_device else bs_cpu
+    pad = 3  # rows of a / c past sum(batch_sizes): must be ignored and left untouched
+    a_cpu = torch.randn(T + pad, d1).bfloat16()
+    if mode == "tn":
+        b_cpu = torch.randn(T + pad, n).bfloat16()
+        c = torch.full((z, d1, n), 7.0, dtype=torch.bfloat16, device="cuda")
+        gg.backend.gmm(a_cpu.cuda(), b_cpu.cuda(), bs, trans_a=True, c=c)
+        want = gmm_oracle.gmm(a_cpu, b_cpu, bs_cpu, trans_a=True)
+        util.assert_close(c, want, rtol=1e-2, atol=1e-2 * max(1.0, float(want.abs().max())) / 8, what="wgrad")
+        for i, s in enumerate(sizes):
+            if s == 0:
+                assert bool((c[i] == 0).all())
+    else:
+        trans_b = mode == "nt"
+        b_cpu = (torch.randn(z, n, d1) if trans_b else torch.randn(z, d1, n)).bfloat16() * 0.25
+        c = torch.full((T + pad, n), 7.0, dtype=torch.bfloat16, device="cuda")
+        gg.backend.gmm(a_cpu.cuda(), b_cpu.cuda(), bs, trans_b=trans_b, c=c)
+        want = gmm_oracle.gmm(a_cpu, b_cpu, bs_cpu, trans_b=trans_b)
+        util.assert_close(c[:T], want[:T], rtol=1e-2, atol=2e-2, what="forward")
+        assert bool((c[T:] == 7.0).all()), "rows past sum(batch_sizes) were written"
+
+
+def test_output_rows_of_neighbour_expert_not_clobbered(gg):
+    """A 1-row expert between two large ones: its tile computes 128 rows but may
+    store one."""
+    torch.manual_seed(2)
+    sizes = [200, 1, 200]
+    a_cpu = torch.randn(401, 64).bfloat16()
+    b_cpu = torch.randn(3, 64, 256).bfloat16() * 0.25
+    out = gg.backend.gmm(a_cpu.cuda(), b_cpu.cuda(), torch.tensor(sizes).cuda())
+    util.assert_close(out, gmm_oracle.gmm(a_cpu, b_cpu, torch.tensor(sizes)), atol=2e-2, what="forward")
+
+
+# ---- argument fill: bit-exact ---------------------------------------------------------
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (False, True), (True, False)])
+@pytest.mark.parametrize("case", ["cfg1", "cfg2", "cfg4", "z1", "z1024", "empty-heavy"])
+def test_fill_offsets_bit_exact(gg, case, trans_a, trans_b):
+    import bench
+    from grouped_gemm_b200 import _capi
+    if case == "cfg1":
+        sizes, d1, n = [128] * 4, 128, 128
+    elif case == "cfg2":
+        sizes, d1, n = bench.mixtral_batch_sizes(), 4096, 14336
+    elif case == "cfg4":
+        sizes, d1, n = bench.fine_grained_batch_sizes(), 7168, 2048  # offsets exceed 2^31
+    elif case == "z1":
+        sizes, d1, n = [12345], 4096, 14336
+    elif case == "z1024":
+        sizes, d1, n = list(np.random.default_rng(5).integers(0, 5000, size=1024)), 6144, 10752
+    else:
+        sizes, d1, n = [0, 0, 7, 0, 0, 0, 1, 0] * 9, 512, 1024
+    bs = torch.tensor([int(s) for s in sizes], dtype=torch.int64, device="cuda")
+    out = torch.full((len(sizes), 9), -1, dtype=torch.int64, device="cuda")
+    rc = _capi.load().b200gmm_fill_offsets(bs.data_ptr(), len(sizes), d1, n, int(trans_a), int(trans_b),
+                                           out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    want = gmm_oracle.fill_offsets(np.asarray(sizes, dtype=np.int64), d1, n, trans_a, trans_b)
+    assert np.array_equal(out.cpu().numpy(), want)
+
+
+# ---- full BASELINE sizes: size-independent properties ------------------------------------
+def _mixtral(gg, trans_b=False):
+    import bench
+    torch.manual_seed(1)
+    sizes = bench.mixtral_batch_sizes()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randn(32768, 4096, device="cuda", generator=g).bfloat16()
+    shape = (8, 14336, 4096) if trans_b else (8, 4096, 14336)
+    b = (torch.randn(*shape, device="cuda", generator=g) * 0.02).bfloat16()
+    return a, b, torch.tensor(sizes, dtype=torch.int64, device="cuda"), sizes
+
+
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_full_size_forward_sampled_rows_and_linearity(gg, trans_b):
+    a, b, bs, sizes = _mixtral(gg, trans_b)
+    out = gg.backend.gmm(a, b, bs, trans_b=trans_b)
+    # (1) oracle on a sample of rows of every expert (first, last, middle of each group)
+    starts = np.concatenate([[0], np.cumsum(sizes)])
+    for e in range(8):
+        rows = sorted({int(starts[e]), int(starts[e + 1]) - 1, int((starts[e] + starts[e + 1]) // 2)})
+        idx = torch.tensor(rows, device="cuda")
+        want = gmm_oracle.gmm(a[idx].cpu(), b[e:e + 1].cpu(), torch.tensor([len(rows)]), trans_b=trans_b)
+        util.assert_close(out[idx], want, what=f"expert {e} sampled rows")
+    # (2) scaling a by 2 is exact in bf16 and fp32, so the result must double bit-for-bit
+    out2 = gg.backend.gmm(a * 2, b, bs, trans_b=trans_b)
+    assert torch.equal(out2, out * 2)
+    # (3) same launch twice is deterministic
+    assert torch.equal(gg.backend.gmm(a, b, bs, trans_b=trans_b), out)
+    # (4) one call over all experts == per-expert calls
+    e = 4
+    solo = gg.backend.gmm(a[starts[e]:starts[e + 1]].contiguous(), b[e:e + 1].contiguous(),
+                          torch.tensor([sizes[e]], device="cuda"), trans_b=trans_b)
+    assert torch.equal(solo, out[starts[e]:starts[e + 1]])
+
+
+def test_full_size_wgrad_properties(gg):
+    a, _, bs, sizes = _mixtral(gg)
+    g = torch.Generator(device="cuda").manual_seed(7)
+    grad = torch.randn(32768, 14336, device="cuda", generator=g).bfloat16()
+    w = gg.backend.gmm(a, grad, bs, trans_a=True)
+    assert w.shape == (8, 4096, 14336)
+    # oracle on a sampled block of each expert's output
+    starts = np.concatenate([[0], np.cumsum(sizes)])
+    for e in (0, 2, 4, 7):
+        rows = slice(int(starts[e]), int(starts[e + 1]))
+        want = (a[rows, 100:164].float().t() @ grad[rows, 5000:5064].float()).cpu()
+        util.assert_close(w[e, 100:164, 5000:5064], want.bfloat16(), rtol=1e-2, atol=1.0, what=f"wgrad expert {e}")
+    # doubling one operand doubles the result exactly; repeat run is bit-identical
+    assert torch.equal(gg.backend.gmm(a * 2, grad, bs, trans_a=True), w * 2)
+    assert torch.equal(gg.backend.gmm(a, grad, bs, trans_a=True), w)
+
+
+def test_fine_grained_moe_config4_reduced_width(gg):
+    """BASELINE config 4's routing (256 experts, Zipf popularity, ~20 % empty,
+    65536 rows) at reduced hidden sizes so the CPU oracle stays in seconds."""
+    import bench
+    sizes = bench.fine_grained_batch_sizes()
+    assert sum(sizes) == 65536 and sum(1 for s in sizes if s == 0) >= 51
+    torch.manual_seed(2)
+    k, n = 256, 264
+    a_cpu = torch.randn(65536, k).bfloat16()
+    b_cpu = (torch.randn(256, k, n) * 0.02).bfloat16()
+    bs_cpu = torch.tensor(sizes, dtype=torch.int64)
+    _check_fwd_bwd(gg, a_cpu, b_cpu, bs_cpu, False, True, ref_stat=False)
+
+
+def test_status_flags_bad_batch_sizes(gg):
+    """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
+    bounds and raises the overflow status bit."""
+    a = torch.randn(100, 64, device="cuda").bfloat16()
+    b = torch.randn(2, 64, 128, device="cuda").bfloat16()
+    c = torch.zeros(100 + 64, 128, device="cuda", dtype=torch.bfloat16)
+    word = gg.backend.backend.device_status("cuda")
+    gg.backend.gmm(a, b, torch.tensor([90, 90], device="cuda"), c=c[:100])
+    assert gg.backend.device_status() & 0x4
+    assert bool((c[100:] == 0).all())
+    word.zero_()
