@@ -525,8 +525,42 @@ def run_multi(args):
     dist.destroy_process_group()
 
 
+def run_profile_case(args):
+    """--profile PASS: allocate only that pass's operands at the Mixtral size
+    and launch it a few times; meant to be wrapped in ncu (one kernel, one
+    captured launch).  Prints the CUDA-event time of the last launch."""
+    from grouped_gemm_b200 import backend
+    dev = torch.device("cuda", 0)
+    z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["k"], MIXTRAL["n"]
+    g = torch.Generator(device=dev).manual_seed(1)
+    bs = torch.tensor(mixtral_batch_sizes(), dtype=torch.int64, device=dev)
+    if args.profile == "fwd":
+        a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+        b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+        c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: backend.gmm(a, b, bs, c=c)
+    elif args.profile == "dgrad":
+        a = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+        b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+        c = torch.empty(rows, k, device=dev, dtype=torch.bfloat16)
+        fn = lambda: backend.gmm(a, b, bs, trans_b=True, c=c)
+    else:
+        a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+        b = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+        c = torch.empty(z, k, n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: backend.gmm(a, b, bs, trans_a=True, c=c)
+    for _ in range(args.profile_launches - 1):
+        fn()
+    ms = time_loop(fn, 1)
+    print(json.dumps({"profile": args.profile, "launches": args.profile_launches, "last_ms": ms,
+                      "device_status": backend.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile", choices=["fwd", "dgrad", "wgrad"], default=None,
+                    help="launch one pass of the Mixtral workload a few times and exit (for ncu)")
+    ap.add_argument("--profile-launches", type=int, default=2)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -539,6 +573,8 @@ def main():
     if args.impl == "reference":
         return run_reference(args)
     world, _, _ = dist_info()
+    if args.profile:
+        return run_profile_case(args)
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path "
                          "(use --impl reference for the CPU baseline)")
