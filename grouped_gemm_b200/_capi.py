@@ -32,9 +32,9 @@ SIGNATURES = {
         _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_void_p]),
     "b200gmm_schedule_host": (_c.c_int, [
-        _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
+        _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_int64, _c.POINTER(_c.c_int64)]),
-    "b200gmm_tile_shape": (_c.c_int, [_c.c_int, _c.c_int, _c.POINTER(_c.c_int)]),
+    "b200gmm_tile_shape": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int)]),
     "b200gmm_launch_count": (_c.c_int64, []),
     "b200gmm_strerror": (_c.c_char_p, [_c.c_int]),
 }
@@ -81,7 +81,7 @@ def launch_count():
     return int(load().b200gmm_launch_count())
 
 
-def tile_shape(trans_a=False, trans_b=False):
+def tile_shape(cluster_ctas=1):
     out = (ctypes.c_int * 3)()
-    check(load().b200gmm_tile_shape(int(trans_a), int(trans_b), out), "b200gmm_tile_shape")
+    check(load().b200gmm_tile_shape(int(cluster_ctas), out), "b200gmm_tile_shape")
     return tuple(out)

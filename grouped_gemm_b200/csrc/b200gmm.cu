@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 
 #include "gmm_kernel.cuh"
@@ -37,8 +38,33 @@ EncodeTiledFn encode_tiled_fn() {
 struct DeviceInfo {
   int sm_count = 0;
   int cc_major = 0;
+  int pair_ctas = 0;  // CTAs a launch of the 2-CTA-cluster variant may use (even, <= sm_count)
   bool attrs_set = false;
 };
+
+template <int MODE, int CTAS>
+cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
+                       __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, c, bs, p, status);
+}
+
+template <int MODE, int CTAS>
+cudaError_t set_smem_attr() {
+  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(kSmemBytes));
+}
 
 // Per-device facts, looked up once.  Index = CUDA device ordinal.
 int device_info(DeviceInfo** out) {
@@ -55,11 +81,30 @@ int device_info(DeviceInfo** out) {
   }
   if (d.cc_major != 10) return B200GMM_EDEVICE;
   if (!d.attrs_set) {
-    const int smem = static_cast<int>(kSmemBytes);
-    if (cudaFuncSetAttribute(gmm_kernel<kNN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(gmm_kernel<kNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(gmm_kernel<kTN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (set_smem_attr<kNN, 1>() != cudaSuccess || set_smem_attr<kNT, 1>() != cudaSuccess ||
+        set_smem_attr<kTN, 1>() != cudaSuccess || set_smem_attr<kNN, 2>() != cudaSuccess ||
+        set_smem_attr<kNT, 2>() != cudaSuccess || set_smem_attr<kTN, 2>() != cudaSuccess)
       return B200GMM_ECUDA;
+    // How many 2-CTA clusters of this kernel the device can hold at once (a GPC
+    // with an odd number of free SMs leaves one out).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(d.sm_count & ~1);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, gmm_kernel<kNN, 2>, &cfg) != cudaSuccess || clusters <= 0) {
+      (void)cudaGetLastError();
+      clusters = 0;
+    }
+    d.pair_ctas = 2 * clusters;
+    if (d.pair_ctas > (d.sm_count & ~1)) d.pair_ctas = d.sm_count & ~1;
     d.attrs_set = true;
   }
   *out = &d;
@@ -89,7 +134,22 @@ int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
   return r == CUDA_SUCCESS ? B200GMM_OK : B200GMM_ETENSORMAP;
 }
 
-int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int trans_b,
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
+}
+
+// Which variant a problem runs on.  Only shapes known on the host may decide
+// (batch_sizes can live on the device): a CTA pair pays off when an expert has,
+// on average, at least a couple of 256-row tiles.  B200GMM_CTAS=1|2 overrides.
+int choose_ctas(int z, int64_t tokens, int64_t d1, int trans_a) {
+  const int forced = env_int("B200GMM_CTAS", 0);
+  if (forced == 1 || forced == 2) return forced;
+  if (trans_a) return d1 >= 256 ? 2 : 1;
+  return (z > 0 && tokens / z >= 512) ? 2 : 1;
+}
+
+int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int trans_b, int ctas,
                   Problem* p) {
   if (trans_a && trans_b) return B200GMM_EINVAL;
   if (z < 0 || tokens < 0 || d1 < 0 || n < 0) return B200GMM_EINVAL;
@@ -103,10 +163,14 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   p->tokens = tokens;
   p->d1 = d1;
   p->n = n;
+  if (ctas != 1 && ctas != 2) return B200GMM_EINVAL;
+  p->tile_m = kBlockM * ctas;
+  p->group_m = env_int("B200GMM_GROUP_M", ctas == 2 ? 8 : 16);
+  if (p->group_m < 1) p->group_m = 1;
   // Upper bound on the tile count must fit the kernel's 32-bit tile index.
   const int64_t nt = (n + kBlockN - 1) / kBlockN;
-  const int64_t row_tiles = trans_a ? int64_t(z) * ((d1 + kBlockM - 1) / kBlockM)
-                                    : (tokens / kBlockM + z);
+  const int64_t row_tiles = trans_a ? int64_t(z) * ((d1 + p->tile_m - 1) / p->tile_m)
+                                    : (tokens / p->tile_m + z);
   if (row_tiles * nt >= (int64_t(1) << 31)) return B200GMM_ELIMIT;
   return B200GMM_OK;
 }
@@ -129,7 +193,8 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
                 int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
                 uint32_t* device_status, void* cuda_stream) {
   Problem p;
-  int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, &p);
+  int ctas = choose_ctas(z, tokens, dim_a1, trans_a);
+  int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p);
   if (rc != B200GMM_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (z == 0) return B200GMM_OK;
@@ -164,6 +229,11 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
   rc = device_info(&dev);
   if (rc != B200GMM_OK) return rc;
 
+  if (ctas == 2 && dev->pair_ctas < 2) {
+    ctas = 1;
+    if ((rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p)) != B200GMM_OK) return rc;
+  }
+
   const int64_t* bs_dev = batch_sizes;
   if (!batch_sizes_on_device) {
     size_t need = 0;
@@ -189,7 +259,7 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
     const uint64_t da[2] = {D1, T};
     const uint32_t ba[2] = {kBlockK, kBlockM};
     const uint64_t db[3] = {D1, N, Z};
-    const uint32_t bb[3] = {kBlockK, kBlockN, 1};
+    const uint32_t bb[3] = {kBlockK, uint32_t(kBlockN / ctas), 1};
     if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
       return rc;
   } else {
@@ -200,15 +270,23 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
       return rc;
   }
 
-  const dim3 grid(dev->sm_count), block(kThreads);
   __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(c);
-  if (p.mode == kNN)
-    gmm_kernel<kNN><<<grid, block, kSmemBytes, stream>>>(map_a, map_b, cp, bs_dev, p, device_status);
-  else if (p.mode == kNT)
-    gmm_kernel<kNT><<<grid, block, kSmemBytes, stream>>>(map_a, map_b, cp, bs_dev, p, device_status);
-  else
-    gmm_kernel<kTN><<<grid, block, kSmemBytes, stream>>>(map_a, map_b, cp, bs_dev, p, device_status);
-  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  cudaError_t err;
+  if (ctas == 2) {
+    const int grid = dev->pair_ctas;
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+  } else {
+    const int grid = dev->sm_count;
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+  }
+  if (err != cudaSuccess) {
+    (void)cudaGetLastError();
+    return B200GMM_ECUDA;
+  }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return B200GMM_OK;
 }
@@ -226,6 +304,8 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a
   p.tokens = 0;
   p.d1 = dim_a1;
   p.n = n;
+  p.tile_m = kBlockM;
+  p.group_m = 1;
   fill_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(batch_sizes_device, p,
                                                                             out_device);
   if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
@@ -234,10 +314,11 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a
 }
 
 int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z, int64_t tokens, int64_t dim_a1,
-                          int64_t n, int trans_a, int trans_b, int64_t* out, int64_t max_tiles,
-                          int64_t* n_tiles) {
+                          int64_t n, int trans_a, int trans_b, int cluster_ctas, int64_t* out,
+                          int64_t max_tiles, int64_t* n_tiles) {
   Problem p;
-  const int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, &p);
+  if (cluster_ctas == 0) cluster_ctas = choose_ctas(z, tokens, dim_a1, trans_a);
+  const int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, cluster_ctas, &p);
   if (rc != B200GMM_OK) return rc;
   if (n_tiles == nullptr || (z > 0 && batch_sizes_host == nullptr)) return B200GMM_EINVAL;
   int64_t count = 0;
@@ -265,9 +346,9 @@ int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z, int64_t tokens
   return B200GMM_OK;
 }
 
-int b200gmm_tile_shape(int trans_a, int trans_b, int* out3) {
-  if (out3 == nullptr || (trans_a && trans_b)) return B200GMM_EINVAL;
-  out3[0] = kBlockM;
+int b200gmm_tile_shape(int cluster_ctas, int* out3) {
+  if (out3 == nullptr || (cluster_ctas != 1 && cluster_ctas != 2)) return B200GMM_EINVAL;
+  out3[0] = kBlockM * cluster_ctas;
   out3[1] = kBlockN;
   out3[2] = kBlockK;
   return B200GMM_OK;

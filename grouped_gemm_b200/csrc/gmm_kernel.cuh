@@ -2,14 +2,23 @@
 //
 // One CTA per SM walks a static round-robin share of all experts' output tiles
 // (schedule.cuh).  Inside a CTA three roles run concurrently:
-//   warp 0      TMA producer: fills a kStages-deep ring of {A tile, B tile} in
-//               shared memory (128-byte swizzle), one mbarrier per stage;
+//   warp 0      TMA producer: fills a ring of {A tile, B tile} stages in shared
+//               memory (128-byte swizzle), one mbarrier per stage;
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (bf16 x bf16 -> fp32 in
 //               TMEM), commits each stage back to the producer and each finished
 //               accumulator to the epilogue; two 256-column accumulators alternate
 //               so the epilogue of tile i overlaps the main loop of tile i+1;
 //   warps 2-5   epilogue: tcgen05.ld the accumulator, round to bf16, store the
 //               rows that exist (ragged last tile of an expert is masked).
+//
+// Two variants, chosen on the host:
+//   CTAS == 1   every CTA owns 128 x 256 output tiles (4 stages of 48 KiB);
+//   CTAS == 2   a pair of CTAs (a 2-CTA cluster on neighbouring SMs) owns
+//               256 x 256 tiles: each CTA stages its own 128 rows of A and HALF of
+//               the B tile, and the leader's tcgen05.mma.cta_group::2 reads both
+//               halves.  That cuts the L2 -> shared-memory traffic per flop by a
+//               third and shrinks a stage to 32 KiB, so six stages fit.  No TMA
+//               multicast is used anywhere.
 //
 // This replaces the CUTLASS GemmGrouped instantiations of the reference
 // (csrc/grouped_gemm.cu:38-81, :324-371), its argument-fill kernel
@@ -26,19 +35,25 @@
 
 namespace b200gmm {
 
-constexpr int kStages = 4;
 constexpr int kThreads = 192;
 constexpr int kMaxExperts = 1024;
 constexpr uint32_t kTmemCols = 512;
-
-constexpr uint32_t kATileBytes = kBlockM * kBlockK * 2;  // 16 KiB
-constexpr uint32_t kBTileBytes = kBlockN * kBlockK * 2;  // 32 KiB
-constexpr uint32_t kStageBytes = kATileBytes + kBTileBytes;
+constexpr int kMaxStages = 6;
 constexpr uint32_t kBoxBytes = 64 * kBlockK * 2;  // one 64-wide MN-major TMA box: 8 KiB
 
+template <int CTAS>
+struct Geometry {
+  static constexpr int kStages = (CTAS == 1) ? 4 : 6;
+  static constexpr int kBCols = kBlockN / CTAS;                 // B columns staged by one CTA
+  static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;    // 16 KiB
+  static constexpr uint32_t kBBytes = kBCols * kBlockK * 2;     // 32 or 16 KiB
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB either way
+};
+
 struct __align__(8) SmemTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -47,7 +62,8 @@ struct __align__(8) SmemTail {
   int tile_start[kMaxExperts + 1];
 };
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + size_t(kStages) * kStageBytes + sizeof(SmemTail);
+constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + Geometry<1>::kRingBytes + sizeof(SmemTail);
+static_assert(Geometry<1>::kRingBytes == Geometry<2>::kRingBytes, "both variants use the same ring size");
 
 // Exclusive prefix sums of batch_sizes (rows) and of per-expert tile counts,
 // by one warp, 32 experts per step with a running carry.  Rows are clamped to
@@ -94,7 +110,7 @@ __device__ __forceinline__ void scan_batch_sizes(const Problem& p, const int64_t
   if (flags != 0u && lane == 0 && status != nullptr && blockIdx.x == 0) atomicOr(status, flags);
 }
 
-// Round-robin walk over this CTA's tiles; every role keeps its own copy.
+// Round-robin walk over this CTA's (or CTA pair's) tiles; every role keeps its own copy.
 struct TileWalker {
   const Problem& p;
   const int* row_start;
@@ -103,8 +119,8 @@ struct TileWalker {
   int e;
   int total;
   int step;
-  __device__ TileWalker(const Problem& p_, const int* rs, const int* ts)
-      : p(p_), row_start(rs), tile_start(ts), t(blockIdx.x), e(0), total(ts[p_.z]), step(gridDim.x) {}
+  __device__ TileWalker(const Problem& p_, const int* rs, const int* ts, int first, int stride)
+      : p(p_), row_start(rs), tile_start(ts), t(first), e(0), total(ts[p_.z]), step(stride) {}
   __device__ __forceinline__ bool next(Tile* out) {
     if (t >= total) return false;
     while (t >= tile_start[e + 1]) ++e;
@@ -114,21 +130,47 @@ struct TileWalker {
   }
 };
 
-template <int MODE>
+// Zero the contraction rows [rem, 64) of every 8 KiB MN-major box of a stage
+// (wgrad, last k-block of an expert), then publish the writes to the async proxy.
+__device__ __forceinline__ void zero_k_tail(uint8_t* stage, uint32_t stage_bytes, int rem, int lane) {
+  const uint32_t skip = static_cast<uint32_t>(rem) * 128u;
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  for (uint32_t box = 0; box < stage_bytes / kBoxBytes; ++box) {
+    uint8_t* bp = stage + box * kBoxBytes;
+    for (uint32_t off = skip + lane * 16u; off < kBoxBytes; off += 512u)
+      *reinterpret_cast<uint4*>(bp + off) = zero;
+  }
+  ptx::fence_proxy_async_smem();
+  __syncwarp();
+}
+
+template <int MODE, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            __nv_bfloat16* __restrict__ c, const int64_t* __restrict__ batch_sizes, const Problem p,
            uint32_t* status) {
+  using G = Geometry<CTAS>;
+  constexpr int kStages = G::kStages;
+  constexpr bool kPair = (CTAS == 2);
+
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;  // 1024-byte aligned: required by the 128-byte swizzle
   const uint32_t stage_base = raw_addr + pad;
-  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + size_t(kStages) * kStageBytes);
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + G::kRingBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;  // 0 = leader (issues the MMAs)
+  const bool leader = (cta_rank == 0u);
   volatile uint32_t* abort_flag = &tail->abort_flag;
+
+  // wgrad with a CTA pair: each CTA's loads complete on its OWN full barrier so
+  // that its warp 1 can zero the k tail before the data is used; the peer then
+  // arrives on the leader's barrier by hand.  Otherwise both CTAs' loads
+  // complete directly on the leader's barrier.
+  constexpr bool kPeerFixup = kPair && (MODE == kTN);
 
   // ------------------------------------------------------------ prologue
   if (warp == 0) {
@@ -136,36 +178,48 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
       for (int s = 0; s < kStages; ++s) {
-        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), (kPeerFixup && leader) ? 2 : 1);
         ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
       }
       for (int i = 0; i < 2; ++i) {
         ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[i]), 1);
-        ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[i]), 4);
+        ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[i]), 4 * CTAS);
       }
       tail->abort_flag = 0u;
       ptx::fence_mbar_init();
     }
     __syncwarp();
   } else if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), kTmemCols);
-    ptx::tmem_relinquish();
+    if (kPair) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&tail->tmem_base), kTmemCols);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), kTmemCols);
+      ptx::tmem_relinquish();
+    }
   } else if (warp == 2) {
     scan_batch_sizes(p, batch_sizes, tail->row_start, tail->tile_start, status, lane);
   }
   ptx::tc_fence_before_sync();
   __syncthreads();
+  if (kPair) ptx::cluster_sync();  // the peer's barriers exist before anything arrives on them
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = tail->tmem_base;
 
-  constexpr bool kAMn = (MODE == kTN);             // A operand MN-major (wgrad reads a^T)
+  constexpr bool kAMn = (MODE == kTN);                 // A operand MN-major (wgrad reads a^T)
   constexpr bool kBMn = (MODE == kNN || MODE == kTN);  // B operand MN-major
-  constexpr uint32_t kIdesc = ptx::make_idesc_bf16(kBlockM, kBlockN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+  constexpr uint32_t kIdesc =
+      ptx::make_idesc_bf16(kBlockM * CTAS, kBlockN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+
+  const int first_tile = kPair ? (blockIdx.x >> 1) : blockIdx.x;
+  const int tile_stride = kPair ? (gridDim.x >> 1) : gridDim.x;
+  const int row_off = static_cast<int>(cta_rank) * kBlockM;  // this CTA's rows inside a pair tile
+  const int col_off = static_cast<int>(cta_rank) * G::kBCols;  // this CTA's share of the B tile
 
   if (warp == 0) {
     // ---------------------------------------------------------- TMA producer
     if (lane == 0) {
-      TileWalker walk(p, tail->row_start, tail->tile_start);
+      TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
       Tile t;
       uint32_t s = 0, ph = 0;
       bool ok = true;
@@ -173,36 +227,67 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
         for (int kb = 0; kb < nkb; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
-          const uint32_t bar = ptx::smem_u32(&tail->full[s]);
-          const uint32_t sa = stage_base + s * kStageBytes;
-          const uint32_t sb = sa + kATileBytes;
-          ptx::mbar_arrive_expect_tx(bar, kStageBytes);
+          const uint32_t local_bar = ptx::smem_u32(&tail->full[s]);
+          const uint32_t sa = stage_base + s * G::kStageBytes;
+          const uint32_t sb = sa + G::kABytes;
           const int k0 = kb * kBlockK;
-          if (MODE == kNN) {
-            ptx::tma_load_2d(sa, &map_a, bar, k0, t.row0);
+          if (!kPair) {
+            ptx::mbar_arrive_expect_tx(local_bar, G::kStageBytes);
+            if (MODE == kNN) {
+              ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
 #pragma unroll
-            for (int j = 0; j < kBlockN / 64; ++j)
-              ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, bar, t.col0 + j * 64, k0, t.expert);
-          } else if (MODE == kNT) {
-            ptx::tma_load_2d(sa, &map_a, bar, k0, t.row0);
-            ptx::tma_load_3d(sb, &map_b, bar, k0, t.col0, t.expert);
+              for (int j = 0; j < G::kBCols / 64; ++j)
+                ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, k0, t.expert);
+            } else if (MODE == kNT) {
+              ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
+              ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0, t.expert);
+            } else {
+              const int r0 = t.k_row0 + k0;
+#pragma unroll
+              for (int j = 0; j < kBlockM / 64; ++j)
+                ptx::tma_load_2d(sa + j * kBoxBytes, &map_a, local_bar, t.row0 + j * 64, r0);
+#pragma unroll
+              for (int j = 0; j < G::kBCols / 64; ++j)
+                ptx::tma_load_2d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, r0);
+            }
           } else {
-            const int r0 = t.k_row0 + k0;
+            // Pair: this CTA stages rows [row0+row_off, +128) of A and columns
+            // [col0+col_off, +128) of B.
+            uint32_t bar;  // shared::cluster address of the barrier the loads complete on
+            if (kPeerFixup) {
+              ptx::mbar_arrive_expect_tx(local_bar, G::kStageBytes);
+              bar = ptx::mapa(local_bar, cta_rank);
+            } else {
+              if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * G::kStageBytes);
+              bar = ptx::mapa(local_bar, 0);
+            }
+            if (MODE == kNN) {
+              ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
 #pragma unroll
-            for (int j = 0; j < kBlockM / 64; ++j)
-              ptx::tma_load_2d(sa + j * kBoxBytes, &map_a, bar, t.row0 + j * 64, r0);
+              for (int j = 0; j < G::kBCols / 64; ++j)
+                ptx::tma_load_3d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, k0,
+                                      t.expert);
+            } else if (MODE == kNT) {
+              ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
+              ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
+            } else {
+              const int r0 = t.k_row0 + k0;
 #pragma unroll
-            for (int j = 0; j < kBlockN / 64; ++j)
-              ptx::tma_load_2d(sb + j * kBoxBytes, &map_b, bar, t.col0 + j * 64, r0);
+              for (int j = 0; j < kBlockM / 64; ++j)
+                ptx::tma_load_2d_pair(sa + j * kBoxBytes, &map_a, bar, t.row0 + row_off + j * 64, r0);
+#pragma unroll
+              for (int j = 0; j < G::kBCols / 64; ++j)
+                ptx::tma_load_2d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, r0);
+            }
           }
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
     }
     __syncwarp();
-  } else if (warp == 1) {
+  } else if (warp == 1 && leader) {
     // ---------------------------------------------------------- MMA issuer
-    TileWalker walk(p, tail->row_start, tail->tile_start);
+    TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
     Tile t;
     uint32_t s = 0, ph = 0, it = 0;
     bool ok = true;
@@ -211,31 +296,24 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       if (nkb == 0) continue;  // empty wgrad expert: the epilogue writes zeros
       const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
       ++it;
-      if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[ab]), aph ^ 1u, abort_flag)) { ok = false; break; }
+      const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
+      if (!(kPair ? ptx::mbar_wait_cluster(te_bar, aph ^ 1u, abort_flag)
+                  : ptx::mbar_wait(te_bar, aph ^ 1u, abort_flag))) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + ab * kBlockN;
       for (int kb = 0; kb < nkb; ++kb) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[s]), ph, abort_flag)) { ok = false; break; }
+        const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
+        if (!(kPeerFixup ? ptx::mbar_wait_cluster(f_bar, ph, abort_flag)
+                         : ptx::mbar_wait(f_bar, ph, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
-        const uint32_t sa = stage_base + s * kStageBytes;
-        const uint32_t sb = sa + kATileBytes;
+        const uint32_t sa = stage_base + s * G::kStageBytes;
+        const uint32_t sb = sa + G::kABytes;
         if (MODE == kTN) {
           // Last k-block of an expert: contraction rows past the expert's end
           // belong to the next expert (or are TMA zero fill).  Zero them in both
-          // operands so they add nothing, then make the writes visible to the
-          // tensor core's (async-proxy) reads.
+          // operands so they add nothing.
           const int rem = t.k_len - kb * kBlockK;
-          if (rem < kBlockK) {
-            const uint32_t skip = rem * 128u;
-            const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-            for (uint32_t box = 0; box < kStageBytes / kBoxBytes; ++box) {
-              uint8_t* bp = smem + size_t(s) * kStageBytes + box * kBoxBytes;
-              for (uint32_t off = skip + lane * 16u; off < kBoxBytes; off += 512u)
-                *reinterpret_cast<uint4*>(bp + off) = zero;
-            }
-            ptx::fence_proxy_async_smem();
-            __syncwarp();
-          }
+          if (rem < kBlockK) zero_k_tail(smem + size_t(s) * G::kStageBytes, G::kStageBytes, rem, lane);
         }
         if (lane == 0) {
           // K-major SW128 operand: 8-row groups 1024 B apart, +32 B per 16-wide k step.
@@ -248,27 +326,58 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           constexpr uint64_t a_step = kAMn ? (2048u >> 4) : (32u >> 4);
           constexpr uint64_t b_step = kBMn ? (2048u >> 4) : (32u >> 4);
 #pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k)
-            ptx::mma_bf16_ss(d_tmem, adesc + k * a_step, bdesc + k * b_step, kIdesc,
-                             (kb | k) != 0 ? 1u : 0u);
-          ptx::mma_commit(ptx::smem_u32(&tail->empty[s]));
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            if (kPair)
+              ptx::mma_bf16_ss_pair(d_tmem, adesc + k * a_step, bdesc + k * b_step, kIdesc,
+                                    (kb | k) != 0 ? 1u : 0u);
+            else
+              ptx::mma_bf16_ss(d_tmem, adesc + k * a_step, bdesc + k * b_step, kIdesc,
+                               (kb | k) != 0 ? 1u : 0u);
+          }
+          if (kPair) ptx::mma_commit_pair(ptx::smem_u32(&tail->empty[s]), 0x3);
+          else ptx::mma_commit(ptx::smem_u32(&tail->empty[s]));
         }
         __syncwarp();
         if (++s == kStages) { s = 0; ph ^= 1u; }
       }
-      if (ok && lane == 0) ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[ab]));
+      if (ok && lane == 0) {
+        if (kPair) ptx::mma_commit_pair(ptx::smem_u32(&tail->tmem_full[ab]), 0x3);
+        else ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[ab]));
+      }
       __syncwarp();
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------- peer CTA, warp 1
+    // Only wgrad has work here: wait for this CTA's own loads, zero the k tail,
+    // then tell the leader that this half of the stage is ready.
+    if (kPeerFixup) {
+      TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+      Tile t;
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      while (ok && walk.next(&t)) {
+        const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+        for (int kb = 0; kb < nkb; ++kb) {
+          const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
+          if (!ptx::mbar_wait(f_bar, ph, abort_flag)) { ok = false; break; }
+          const int rem = t.k_len - kb * kBlockK;
+          if (rem < kBlockK) zero_k_tail(smem + size_t(s) * G::kStageBytes, G::kStageBytes, rem, lane);
+          if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(f_bar, 0));
+          __syncwarp();
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
     }
   } else {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    TileWalker walk(p, tail->row_start, tail->tile_start);
+    TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
     Tile t;
     uint32_t it = 0;
     bool ok = true;
     while (ok && walk.next(&t)) {
       const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
-      const int r = q * 32 + lane;
+      const int r = row_off + q * 32 + lane;  // row inside the (pair) tile
       const bool row_ok = r < t.valid_rows;
       const int64_t out_row = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0 + r)
                                             : (int64_t(t.row0) + r);
@@ -314,7 +423,11 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[ab]));
+      if (lane == 0) {
+        const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
+        if (kPair) ptx::mbar_arrive_cluster(ptx::mapa(te_bar, 0));
+        else ptx::mbar_arrive(te_bar);
+      }
     }
   }
 
@@ -328,9 +441,13 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     while (ptx::globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
     __syncthreads();
   }
+  // Neither CTA of a pair may retire while the other can still signal its
+  // barriers or read its shared memory.
+  if (kPair) ptx::cluster_sync();
   if (warp == 1) {
     ptx::tc_fence_after_sync();
-    ptx::tmem_dealloc(tmem_base, kTmemCols);
+    if (kPair) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+    else ptx::tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 

@@ -24,10 +24,9 @@ enum Mode : int {
   kTN = 2,  // c[i]      = a[rows_i]^T @ b[rows_i] (wgrad)
 };
 
-constexpr int kBlockM = 128;  // output tile rows   (UMMA M)
+constexpr int kBlockM = 128;  // output rows per CTA (UMMA M per CTA)
 constexpr int kBlockN = 256;  // output tile cols   (UMMA N)
 constexpr int kBlockK = 64;   // k depth per pipeline stage = one 128-byte swizzle row of bf16
-constexpr int kGroupM = 8;    // row-tiles swept together across the columns (L2 reuse of b)
 
 struct Problem {
   int mode;
@@ -35,13 +34,15 @@ struct Problem {
   int64_t tokens;  // rows of a
   int64_t d1;      // a.shape[1]: k for NN/NT, m for TN
   int64_t n;       // output columns
+  int tile_m;      // output rows per scheduled tile: 128 (one CTA) or 256 (a CTA pair)
+  int group_m;     // row-tiles swept together across the columns (L2 reuse of b)
 };
 
 struct Tile {
   int expert;
   int row0;        // NN/NT: first row of a/c (global); TN: first row of c[expert]
   int col0;        // first output column
-  int valid_rows;  // rows of this tile that exist in the output
+  int valid_rows;  // rows of this tile (of tile_m) that exist in the output
   int k_row0;      // TN: first contraction row in a/b (global); else 0
   int k_len;       // contraction length (k, or batch_sizes[expert] for TN)
 };
@@ -54,17 +55,17 @@ B200GMM_HD int col_tiles(const Problem& p) { return ceil_div_i(p.n, kBlockN); }
 // need their zeros written, csrc/fill_arguments.cuh:100-119).
 B200GMM_HD int expert_tiles(const Problem& p, int64_t rows) {
   const int nt = col_tiles(p);
-  if (p.mode == kTN) return ceil_div_i(p.d1, kBlockM) * nt;
-  return ceil_div_i(rows, kBlockM) * nt;
+  if (p.mode == kTN) return ceil_div_i(p.d1, p.tile_m) * nt;
+  return ceil_div_i(rows, p.tile_m) * nt;
 }
 
-// Within one expert: walk kGroupM row-tiles down, then step one column-tile
+// Within one expert: walk group_m row-tiles down, then step one column-tile
 // right, so that concurrently running CTAs share a and b panels in L2.
-B200GMM_HD void decode_in_expert(int local, int row_tiles, int nt, int* mi, int* ni) {
-  const int group_span = kGroupM * nt;
+B200GMM_HD void decode_in_expert(int local, int row_tiles, int nt, int group_m, int* mi, int* ni) {
+  const int group_span = group_m * nt;
   const int g = local / group_span;
-  const int first = g * kGroupM;
-  const int gm = (row_tiles - first) < kGroupM ? (row_tiles - first) : kGroupM;
+  const int first = g * group_m;
+  const int gm = (row_tiles - first) < group_m ? (row_tiles - first) : group_m;
   const int r = local - g * group_span;
   *mi = first + r % gm;
   *ni = r / gm;
@@ -78,19 +79,19 @@ B200GMM_HD Tile make_tile(const Problem& p, int expert, int local, int rs, int r
   const int nt = col_tiles(p);
   int mi, ni;
   if (p.mode == kTN) {
-    const int mt = ceil_div_i(p.d1, kBlockM);
-    decode_in_expert(local, mt, nt, &mi, &ni);
-    t.row0 = mi * kBlockM;
+    const int mt = ceil_div_i(p.d1, p.tile_m);
+    decode_in_expert(local, mt, nt, p.group_m, &mi, &ni);
+    t.row0 = mi * p.tile_m;
     const int left = static_cast<int>(p.d1) - t.row0;
-    t.valid_rows = left < kBlockM ? left : kBlockM;
+    t.valid_rows = left < p.tile_m ? left : p.tile_m;
     t.k_row0 = rs;
     t.k_len = re - rs;
   } else {
-    const int mt = ceil_div_i(re - rs, kBlockM);
-    decode_in_expert(local, mt, nt, &mi, &ni);
-    t.row0 = rs + mi * kBlockM;
+    const int mt = ceil_div_i(re - rs, p.tile_m);
+    decode_in_expert(local, mt, nt, p.group_m, &mi, &ni);
+    t.row0 = rs + mi * p.tile_m;
     const int left = re - t.row0;
-    t.valid_rows = left < kBlockM ? left : kBlockM;
+    t.valid_rows = left < p.tile_m ? left : p.tile_m;
     t.k_row0 = 0;
     t.k_len = static_cast<int>(p.d1);
   }

@@ -56,6 +56,10 @@ int b200gmm_workspace_bytes(int z, size_t* out_bytes);
 
 /*
  * The grouped GEMM itself: one persistent kernel launch for all experts.
+ * Two kernel variants exist (tiles owned by one CTA, or by a pair of CTAs on
+ * neighbouring SMs); the choice depends only on the shapes passed here and can
+ * be forced with the environment variable B200GMM_CTAS=1|2.  B200GMM_GROUP_M
+ * overrides how many row-tiles are swept together across the columns.
  * Replaces grouped_gemm::GroupedGemm (csrc/grouped_gemm.cu:470-564, prototype
  * csrc/grouped_gemm.h:5-9) together with the argument fill
  * (csrc/fill_arguments.cuh:34-131) that precedes the CUTLASS launch.
@@ -105,17 +109,20 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z,
  * __host__ __device__ code as the kernel).  Writes, for every tile index in
  * launch order, {expert, row0, col0, valid_rows, k_blocks} as int64 into `out`
  * (5 per tile, at most `max_tiles` tiles) and the tile count into *n_tiles.
- * Pure host arithmetic; needs no GPU.  It has no counterpart in the reference,
- * whose schedule lives inside CUTLASS (GroupScheduleMode::kDeviceOnly,
- * csrc/grouped_gemm.cu:256-259).
+ * `cluster_ctas` selects the kernel variant: 1 (each CTA owns 128-row tiles),
+ * 2 (a pair of CTAs owns 256-row tiles) or 0 (whatever b200gmm_run would pick
+ * for these shapes).  Pure host arithmetic; needs no GPU.  It has no
+ * counterpart in the reference, whose schedule lives inside CUTLASS
+ * (GroupScheduleMode::kDeviceOnly, csrc/grouped_gemm.cu:256-259).
  */
 int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z,
                           int64_t tokens, int64_t dim_a1, int64_t n,
-                          int trans_a, int trans_b,
+                          int trans_a, int trans_b, int cluster_ctas,
                           int64_t* out, int64_t max_tiles, int64_t* n_tiles);
 
-/* Tile shape the kernels use: out[0]=rows, out[1]=cols, out[2]=k depth. */
-int b200gmm_tile_shape(int trans_a, int trans_b, int* out3);
+/* Tile shape of a kernel variant (cluster_ctas = 1 or 2): out[0]=rows,
+ * out[1]=cols, out[2]=k depth per pipeline stage. */
+int b200gmm_tile_shape(int cluster_ctas, int* out3);
 
 /* Number of kernels this library has launched in this process (all entry
  * points), for launch accounting in benchmarks. */

@@ -32,7 +32,8 @@ def test_header_symbols_all_exported():
 def test_strerror_and_tile_shape():
     assert _capi.strerror(0) == "ok"
     assert "trans_a" in _capi.strerror(-1)
-    assert _capi.tile_shape() == (128, 256, 64)
+    assert _capi.tile_shape(1) == (128, 256, 64)
+    assert _capi.tile_shape(2) == (256, 256, 64)
 
 
 def test_workspace_bytes():
@@ -68,17 +69,17 @@ def test_run_with_no_work_is_ok_without_gpu():
     assert lib.b200gmm_run(None, None, None, bs.ctypes.data, 0, 4, 0, 128, 128, 0, 0, None, 0, None, None) == 0
 
 
-def _schedule(sizes, tokens, d1, n, trans_a, trans_b):
+def _schedule(sizes, tokens, d1, n, trans_a, trans_b, ctas=1):
     lib = _capi.load()
     bs = np.asarray(sizes, dtype=np.int64)
     count = ctypes.c_int64(0)
     ptr = bs.ctypes.data if len(sizes) else None
-    rc = lib.b200gmm_schedule_host(ptr, len(sizes), tokens, d1, n, trans_a, trans_b, None, 0,
+    rc = lib.b200gmm_schedule_host(ptr, len(sizes), tokens, d1, n, trans_a, trans_b, ctas, None, 0,
                                    ctypes.byref(count))
     assert rc == 0
     out = np.zeros((count.value, 5), dtype=np.int64)
-    rc = lib.b200gmm_schedule_host(ptr, len(sizes), tokens, d1, n, trans_a, trans_b, out.ctypes.data,
-                                   count.value, ctypes.byref(count))
+    rc = lib.b200gmm_schedule_host(ptr, len(sizes), tokens, d1, n, trans_a, trans_b, ctas,
+                                   out.ctypes.data, count.value, ctypes.byref(count))
     assert rc == 0
     return out
 
@@ -96,13 +97,15 @@ SIZE_SETS = [
 @pytest.mark.parametrize("sizes", SIZE_SETS)
 @pytest.mark.parametrize("trans_b", [0, 1])
 @pytest.mark.parametrize("n", [128, 256, 328, 1536])
-def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n):
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n, ctas):
     tokens = sum(sizes)
-    tiles = _schedule(sizes, tokens, 512, n, 0, trans_b)
+    tile_m = 128 * ctas
+    tiles = _schedule(sizes, tokens, 512, n, 0, trans_b, ctas)
     cover = np.zeros((tokens, (n + 255) // 256), dtype=np.int32)
     starts = np.concatenate([[0], np.cumsum(sizes)])
     for e, row0, col0, valid, kblocks in tiles:
-        assert 0 < valid <= 128 and col0 % 256 == 0 and col0 < n
+        assert 0 < valid <= tile_m and col0 % 256 == 0 and col0 < n
         assert starts[e] <= row0 and row0 + valid <= starts[e + 1], "tile leaves its expert's rows"
         assert kblocks == 512 // 64
         cover[row0:row0 + valid, col0 // 256] += 1
@@ -112,22 +115,33 @@ def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n):
 
 
 @pytest.mark.parametrize("sizes", SIZE_SETS)
-def test_schedule_wgrad_full_grid_for_every_expert(sizes):
+@pytest.mark.parametrize("ctas", [1, 2])
+def test_schedule_wgrad_full_grid_for_every_expert(sizes, ctas):
     tokens, m, n = sum(sizes), 320, 520
-    tiles = _schedule(sizes, tokens, m, n, 1, 0)
-    per_expert = ((m + 127) // 128) * ((n + 255) // 256)
+    tile_m = 128 * ctas
+    tiles = _schedule(sizes, tokens, m, n, 1, 0, ctas)
+    per_expert = ((m + tile_m - 1) // tile_m) * ((n + 255) // 256)
     assert len(tiles) == per_expert * len(sizes)
     for e, size in enumerate(sizes):
         mine = tiles[tiles[:, 0] == e]
-        cover = np.zeros(((m + 127) // 128, (n + 255) // 256), dtype=np.int32)
+        cover = np.zeros(((m + tile_m - 1) // tile_m, (n + 255) // 256), dtype=np.int32)
         for _, row0, col0, valid, kblocks in mine:
-            assert valid == min(128, m - row0)
+            assert valid == min(tile_m, m - row0)
             assert kblocks == (size + 63) // 64  # 0 for an empty expert: zero-fill tile
-            cover[row0 // 128, col0 // 256] += 1
+            cover[row0 // tile_m, col0 // 256] += 1
         assert (cover == 1).all()
 
 
 def test_schedule_clamps_rows_past_tokens():
     # sum(batch_sizes) > tokens must never schedule a row >= tokens
-    tiles = _schedule([100, 100, 100], 150, 128, 256, 0, 0)
-    assert int((tiles[:, 1] + tiles[:, 3]).max()) <= 150
+    for ctas in (1, 2):
+        tiles = _schedule([100, 100, 100], 150, 128, 256, 0, 0, ctas)
+        assert int((tiles[:, 1] + tiles[:, 3]).max()) <= 150
+
+
+def test_variant_choice_depends_on_shapes_only():
+    """cluster_ctas=0 asks for the variant b200gmm_run would use: pairs for
+    experts with many rows, single CTAs for fine-grained groups."""
+    big = _schedule([4096] * 8, 32768, 512, 512, 0, 0, 0)
+    small = _schedule([64] * 64, 4096, 512, 512, 0, 0, 0)
+    assert int(big[:, 3].max()) == 256 and int(small[:, 3].max()) == 64
