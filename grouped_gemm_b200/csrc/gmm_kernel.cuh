@@ -297,14 +297,12 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
       ++it;
       const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
-      if (!(kPair ? ptx::mbar_wait_cluster(te_bar, aph ^ 1u, abort_flag)
-                  : ptx::mbar_wait(te_bar, aph ^ 1u, abort_flag))) { ok = false; break; }
+      if (!ptx::mbar_wait(te_bar, aph ^ 1u, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + ab * kBlockN;
       for (int kb = 0; kb < nkb; ++kb) {
         const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
-        if (!(kPeerFixup ? ptx::mbar_wait_cluster(f_bar, ph, abort_flag)
-                         : ptx::mbar_wait(f_bar, ph, abort_flag))) { ok = false; break; }
+        if (!ptx::mbar_wait(f_bar, ph, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t sa = stage_base + s * G::kStageBytes;
         const uint32_t sb = sa + G::kABytes;
@@ -361,7 +359,10 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
           if (!ptx::mbar_wait(f_bar, ph, abort_flag)) { ok = false; break; }
           const int rem = t.k_len - kb * kBlockK;
-          if (rem < kBlockK) zero_k_tail(smem + size_t(s) * G::kStageBytes, G::kStageBytes, rem, lane);
+          if (rem < kBlockK) {
+            zero_k_tail(smem + size_t(s) * G::kStageBytes, G::kStageBytes, rem, lane);
+            ptx::fence_acq_rel_cluster();  // the zeros are in place before the leader may issue
+          }
           if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(f_bar, 0));
           __syncwarp();
           if (++s == kStages) { s = 0; ph ^= 1u; }

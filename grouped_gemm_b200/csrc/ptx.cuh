@@ -188,41 +188,15 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
 }
 
 // Arrive on an mbarrier that may live in the peer CTA (shared::cluster address).
+// Default semantics (release at CTA scope): a cluster-scope release on every
+// pipeline stage costs a round trip per stage.  Where the arrival must publish
+// generic-proxy writes to the peer, call fence_acq_rel_cluster() first.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar)
-               : "memory");
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 
-__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
-
-// Bounded wait like mbar_wait(), with cluster-scope acquire: for barriers that
-// threads of the peer CTA arrive on.
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
-                                                  volatile uint32_t* abort_flag) {
-  if (mbar_try_wait_cluster(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait_cluster(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1u;
-        return false;
-      }
-    }
-  }
+__device__ __forceinline__ void fence_acq_rel_cluster() {
+  asm volatile("fence.acq_rel.cluster;" ::: "memory");
 }
 
 // TMA loads issued by either CTA of a pair; the mbarrier operand is a

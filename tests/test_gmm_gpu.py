@@ -25,9 +25,13 @@ def gg():
     return grouped_gemm_b200
 
 
-@pytest.fixture(autouse=True)
-def _clean_status(gg):
-    yield
+@pytest.fixture(autouse=True, params=["1", "2"], ids=["one-cta", "cta-pair"])
+def _variant(request, monkeypatch, gg):
+    """Every test runs on both kernel variants: tiles owned by one CTA, and tiles
+    owned by a pair of CTAs (tcgen05 cta_group::2).  The library reads the
+    variable on each call."""
+    monkeypatch.setenv("B200GMM_CTAS", request.param)
+    yield request.param
     assert gg.backend.device_status() == 0, "a kernel raised a status bit (timeout / bad sizes)"
 
 
