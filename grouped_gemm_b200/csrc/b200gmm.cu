@@ -44,7 +44,8 @@ struct DeviceInfo {
 
 template <int MODE, int CTAS>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                       __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status) {
+                       __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
+                       CUtensorMap* slots) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
@@ -57,7 +58,7 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, c, bs, p, status);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, c, bs, p, status, slots);
 }
 
 template <int MODE, int CTAS>
@@ -175,7 +176,12 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   return B200GMM_OK;
 }
 
-size_t round16(size_t x) { return (x + 15) & ~size_t(15); }
+size_t round128(size_t x) { return (x + 127) & ~size_t(127); }
+
+// Workspace layout: [0, 8z) device copy of batch_sizes; then, 128-byte aligned,
+// kMaxCtas x kMapSlots x {a, b} tensor maps edited by the wgrad kernel.
+size_t maps_offset(int z) { return round128(size_t(z) * sizeof(int64_t) + 16); }
+size_t maps_bytes() { return size_t(kMaxCtas) * kMapSlots * 2 * sizeof(CUtensorMap); }
 
 }  // namespace
 
@@ -184,7 +190,7 @@ extern "C" {
 int b200gmm_workspace_bytes(int z, size_t* out_bytes) {
   if (out_bytes == nullptr || z < 0) return B200GMM_EINVAL;
   if (z > kMaxExperts) return B200GMM_ELIMIT;
-  *out_bytes = round16(size_t(z) * sizeof(int64_t)) + 16;
+  *out_bytes = maps_offset(z) + maps_bytes();
   return B200GMM_OK;
 }
 
@@ -234,12 +240,14 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
     if ((rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p)) != B200GMM_OK) return rc;
   }
 
+  size_t need = 0;
+  b200gmm_workspace_bytes(z, &need);
+  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 127))
+    return B200GMM_EWORKSPACE;
+  CUtensorMap* slots = reinterpret_cast<CUtensorMap*>(static_cast<char*>(workspace) + maps_offset(z));
+
   const int64_t* bs_dev = batch_sizes;
   if (!batch_sizes_on_device) {
-    size_t need = 0;
-    b200gmm_workspace_bytes(z, &need);
-    if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 15))
-      return B200GMM_EWORKSPACE;
     if (cudaMemcpyAsync(workspace, batch_sizes, size_t(z) * sizeof(int64_t), cudaMemcpyHostToDevice,
                         stream) != cudaSuccess)
       return B200GMM_ECUDA;
@@ -273,15 +281,15 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
   __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(c);
   cudaError_t err;
   if (ctas == 2) {
-    const int grid = dev->pair_ctas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+    const int grid = dev->pair_ctas < kMaxCtas ? dev->pair_ctas : kMaxCtas;
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
   } else {
-    const int grid = dev->sm_count;
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status);
+    const int grid = dev->sm_count < kMaxCtas ? dev->sm_count : kMaxCtas;
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
@@ -362,7 +370,7 @@ const char* b200gmm_strerror(int code) {
     case B200GMM_EINVAL: return "invalid argument (null pointer, negative size, or trans_a and trans_b both set)";
     case B200GMM_EALIGN: return "row lengths must be multiples of 8 bf16 elements and pointers 16-byte aligned";
     case B200GMM_ELIMIT: return "too many experts (max 1024), too many tiles, or a dimension >= 2^31";
-    case B200GMM_EWORKSPACE: return "workspace missing, smaller than b200gmm_workspace_bytes(z), or not 16-byte aligned";
+    case B200GMM_EWORKSPACE: return "workspace missing, smaller than b200gmm_workspace_bytes(z), or not 128-byte aligned";
     case B200GMM_ECUDA: return "a CUDA runtime or driver call failed";
     case B200GMM_ETENSORMAP: return "cuTensorMapEncodeTiled rejected a tensor (address, stride or extent)";
     case B200GMM_EDEVICE: return "current device is not compute capability 10.x (B200, sm_100a)";

@@ -39,7 +39,15 @@ constexpr int kThreads = 192;
 constexpr int kMaxExperts = 1024;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 6;
+static_assert(8 > kMaxStages, "kMapSlots must exceed the number of pipeline stages");
 constexpr uint32_t kBoxBytes = 64 * kBlockK * 2;  // one 64-wide MN-major TMA box: 8 KiB
+// wgrad keeps private, editable copies of its two tensor maps in the caller's
+// workspace: kMapSlots {a, b} pairs per CTA, used round-robin.  A slot is edited
+// again only after kMapSlots further edits, each followed by at least one load,
+// i.e. after more loads than the ring has stages, so no load still in flight
+// reads a map while it changes.
+constexpr int kMapSlots = 8;
+constexpr int kMaxCtas = 256;  // workspace is sized for this many CTAs
 
 template <int CTAS>
 struct Geometry {
@@ -130,25 +138,11 @@ struct TileWalker {
   }
 };
 
-// Zero the contraction rows [rem, 64) of every 8 KiB MN-major box of a stage
-// (wgrad, last k-block of an expert), then publish the writes to the async proxy.
-__device__ __forceinline__ void zero_k_tail(uint8_t* stage, uint32_t stage_bytes, int rem, int lane) {
-  const uint32_t skip = static_cast<uint32_t>(rem) * 128u;
-  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-  for (uint32_t box = 0; box < stage_bytes / kBoxBytes; ++box) {
-    uint8_t* bp = stage + box * kBoxBytes;
-    for (uint32_t off = skip + lane * 16u; off < kBoxBytes; off += 512u)
-      *reinterpret_cast<uint4*>(bp + off) = zero;
-  }
-  ptx::fence_proxy_async_smem();
-  __syncwarp();
-}
-
 template <int MODE, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            __nv_bfloat16* __restrict__ c, const int64_t* __restrict__ batch_sizes, const Problem p,
-           uint32_t* status) {
+           uint32_t* status, CUtensorMap* map_slots) {
   using G = Geometry<CTAS>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
@@ -166,19 +160,13 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   const bool leader = (cta_rank == 0u);
   volatile uint32_t* abort_flag = &tail->abort_flag;
 
-  // wgrad with a CTA pair: each CTA's loads complete on its OWN full barrier so
-  // that its warp 1 can zero the k tail before the data is used; the peer then
-  // arrives on the leader's barrier by hand.  Otherwise both CTAs' loads
-  // complete directly on the leader's barrier.
-  constexpr bool kPeerFixup = kPair && (MODE == kTN);
-
   // ------------------------------------------------------------ prologue
   if (warp == 0) {
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
       for (int s = 0; s < kStages; ++s) {
-        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), (kPeerFixup && leader) ? 2 : 1);
+        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
         ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
       }
       for (int i = 0; i < 2; ++i) {
@@ -218,13 +206,45 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
 
   if (warp == 0) {
     // ---------------------------------------------------------- TMA producer
+    CUtensorMap* my_maps = map_slots + size_t(blockIdx.x) * (kMapSlots * 2);
+    if (MODE == kTN) {
+      // Private copies of both maps in every slot (2 KiB per CTA), by the whole warp.
+      const uint4* src_a = reinterpret_cast<const uint4*>(&map_a);
+      const uint4* src_b = reinterpret_cast<const uint4*>(&map_b);
+      uint4* dst = reinterpret_cast<uint4*>(my_maps);
+      for (int i = lane; i < kMapSlots * 2 * 8; i += 32) {
+        const int which = (i >> 3) & 1;  // 8 x 16 bytes per map; maps alternate a, b
+        dst[i] = which ? src_b[i & 7] : src_a[i & 7];
+      }
+      __syncwarp();
+    }
     if (lane == 0) {
       TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
       Tile t;
       uint32_t s = 0, ph = 0;
       bool ok = true;
+      int slot = 0, slot_expert = -1;
+      const CUtensorMap* tn_a = my_maps;
+      const CUtensorMap* tn_b = my_maps + 1;
       while (ok && walk.next(&t)) {
         const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+        if (MODE == kTN && nkb > 0 && t.expert != slot_expert) {
+          // New expert: clip the row extent of a and b at its last row, so that
+          // the rows a k-block would read from the next expert are out of bounds
+          // for TMA and arrive as zeros.
+          slot_expert = t.expert;
+          slot = (slot + 1) % kMapSlots;
+          CUtensorMap* ea = my_maps + slot * 2;
+          CUtensorMap* eb = ea + 1;
+          const uint32_t rows_end = static_cast<uint32_t>(t.k_row0 + t.k_len);
+          ptx::tensormap_set_dim1(ea, rows_end);
+          ptx::tensormap_set_dim1(eb, rows_end);
+          ptx::fence_tensormap_release();
+          ptx::fence_tensormap_acquire(ea);
+          ptx::fence_tensormap_acquire(eb);
+          tn_a = ea;
+          tn_b = eb;
+        }
         for (int kb = 0; kb < nkb; ++kb) {
           if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t local_bar = ptx::smem_u32(&tail->full[s]);
@@ -245,22 +265,17 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               const int r0 = t.k_row0 + k0;
 #pragma unroll
               for (int j = 0; j < kBlockM / 64; ++j)
-                ptx::tma_load_2d(sa + j * kBoxBytes, &map_a, local_bar, t.row0 + j * 64, r0);
+                ptx::tma_load_2d(sa + j * kBoxBytes, tn_a, local_bar, t.row0 + j * 64, r0);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
-                ptx::tma_load_2d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, r0);
+                ptx::tma_load_2d(sb + j * kBoxBytes, tn_b, local_bar, t.col0 + j * 64, r0);
             }
           } else {
             // Pair: this CTA stages rows [row0+row_off, +128) of A and columns
             // [col0+col_off, +128) of B.
-            uint32_t bar;  // shared::cluster address of the barrier the loads complete on
-            if (kPeerFixup) {
-              ptx::mbar_arrive_expect_tx(local_bar, G::kStageBytes);
-              bar = ptx::mapa(local_bar, cta_rank);
-            } else {
-              if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * G::kStageBytes);
-              bar = ptx::mapa(local_bar, 0);
-            }
+            // Both CTAs' loads complete on the leader's barrier (shared::cluster address).
+            if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * G::kStageBytes);
+            const uint32_t bar = ptx::mapa(local_bar, 0);
             if (MODE == kNN) {
               ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
 #pragma unroll
@@ -274,10 +289,10 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               const int r0 = t.k_row0 + k0;
 #pragma unroll
               for (int j = 0; j < kBlockM / 64; ++j)
-                ptx::tma_load_2d_pair(sa + j * kBoxBytes, &map_a, bar, t.row0 + row_off + j * 64, r0);
+                ptx::tma_load_2d_pair(sa + j * kBoxBytes, tn_a, bar, t.row0 + row_off + j * 64, r0);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
-                ptx::tma_load_2d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, r0);
+                ptx::tma_load_2d_pair(sb + j * kBoxBytes, tn_b, bar, t.col0 + col_off + j * 64, r0);
             }
           }
           if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -306,13 +321,6 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         ptx::tc_fence_after_sync();
         const uint32_t sa = stage_base + s * G::kStageBytes;
         const uint32_t sb = sa + G::kABytes;
-        if (MODE == kTN) {
-          // Last k-block of an expert: contraction rows past the expert's end
-          // belong to the next expert (or are TMA zero fill).  Zero them in both
-          // operands so they add nothing.
-          const int rem = t.k_len - kb * kBlockK;
-          if (rem < kBlockK) zero_k_tail(smem + size_t(s) * G::kStageBytes, G::kStageBytes, rem, lane);
-        }
         if (lane == 0) {
           // K-major SW128 operand: 8-row groups 1024 B apart, +32 B per 16-wide k step.
           // MN-major SW128 operand: 64-wide boxes 8 KiB apart (LBO), 8-k-row groups
@@ -345,30 +353,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       __syncwarp();
     }
   } else if (warp == 1) {
-    // ---------------------------------------------------------- peer CTA, warp 1
-    // Only wgrad has work here: wait for this CTA's own loads, zero the k tail,
-    // then tell the leader that this half of the stage is ready.
-    if (kPeerFixup) {
-      TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
-      Tile t;
-      uint32_t s = 0, ph = 0;
-      bool ok = true;
-      while (ok && walk.next(&t)) {
-        const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
-        for (int kb = 0; kb < nkb; ++kb) {
-          const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
-          if (!ptx::mbar_wait(f_bar, ph, abort_flag)) { ok = false; break; }
-          const int rem = t.k_len - kb * kBlockK;
-          if (rem < kBlockK) {
-            zero_k_tail(smem + size_t(s) * G::kStageBytes, G::kStageBytes, rem, lane);
-            ptx::fence_acq_rel_cluster();  // the zeros are in place before the leader may issue
-          }
-          if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa(f_bar, 0));
-          __syncwarp();
-          if (++s == kStages) { s = 0; ph ^= 1u; }
-        }
-      }
-    }
+    // peer CTA of a pair: the leader issues the MMAs for both
   } else {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant this warp may read

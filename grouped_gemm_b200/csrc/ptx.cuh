@@ -188,15 +188,10 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
 }
 
 // Arrive on an mbarrier that may live in the peer CTA (shared::cluster address).
-// Default semantics (release at CTA scope): a cluster-scope release on every
-// pipeline stage costs a round trip per stage.  Where the arrival must publish
-// generic-proxy writes to the peer, call fence_acq_rel_cluster() first.
+// Default semantics (release at CTA scope): a cluster-scope release costs a
+// round trip per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-__device__ __forceinline__ void fence_acq_rel_cluster() {
-  asm volatile("fence.acq_rel.cluster;" ::: "memory");
 }
 
 // TMA loads issued by either CTA of a pair; the mbarrier operand is a
@@ -260,6 +255,26 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t bar, uint16_t cta_mask)
       "[%0], %1;" ::"r"(bar),
       "h"(cta_mask)
       : "memory");
+}
+
+// ---------------------------------------------------------------- device-side tensor-map edits
+// Overwrite the extent of dimension 1 of a tensor map that lives in global
+// memory, then publish the edit to the TMA unit (tensormap proxy).  Used by the
+// wgrad producer to clip the row extent of a and b at the current expert's last
+// row, so that TMA's own out-of-bounds fill zeroes the rest of a k-block.
+__device__ __forceinline__ void tensormap_set_dim1(void* gmap, uint32_t extent) {
+  asm volatile("tensormap.replace.tile.global_dim.global.b1024.b32 [%0], 1, %1;" ::"l"(
+                   reinterpret_cast<uint64_t>(gmap)),
+               "r"(extent)
+               : "memory");
+}
+__device__ __forceinline__ void fence_tensormap_release() {
+  asm volatile("fence.proxy.tensormap::generic.release.gpu;" ::: "memory");
+}
+__device__ __forceinline__ void fence_tensormap_acquire(const void* gmap) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(
+                   reinterpret_cast<uint64_t>(gmap))
+               : "memory");
 }
 
 // ---------------------------------------------------------------- descriptors

@@ -46,9 +46,12 @@ extern "C" {
 #define B200GMM_FILL_FIELDS 9
 
 /*
- * Bytes of device scratch b200gmm_run needs for `z` experts.  The scratch holds
- * a device copy of batch_sizes (when the caller's copy is in host memory) and
- * the status word.  Replaces the seven per-call torch::empty scratch tensors of
+ * Bytes of device scratch b200gmm_run needs for `z` experts (about 0.5 MB).
+ * The scratch holds a device copy of batch_sizes (when the caller's copy is in
+ * host memory) and, for trans_a, per-CTA copies of the two TMA tensor maps whose
+ * row extent the kernel clips at each expert's last row.  Two calls that may run
+ * at the same time need separate workspaces.
+ * Replaces the seven per-call torch::empty scratch tensors of
  * csrc/grouped_gemm.cu:119-138 (MakeArgumentsOnDevice) and the seven H2D copies
  * of csrc/grouped_gemm.cu:83-94, :209-218 (CopyToDevice).
  */
@@ -81,7 +84,7 @@ int b200gmm_workspace_bytes(int z, size_t* out_bytes);
  * synchronisation).
  *
  * `workspace` is device memory of at least b200gmm_workspace_bytes(z) bytes,
- * 16-byte aligned, owned by the caller and reusable once the stream has passed
+ * 128-byte aligned, owned by the caller and reusable once the stream has passed
  * this call.  If `device_status` is non-NULL it must point to a 4-byte device
  * word that the kernel ORs B200GMM_STATUS_* bits into (the caller clears it).
  */

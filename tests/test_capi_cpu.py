@@ -37,9 +37,10 @@ def test_strerror_and_tile_shape():
 
 
 def test_workspace_bytes():
-    assert _capi.workspace_bytes(0) == 16
-    assert _capi.workspace_bytes(8) == 80
-    assert _capi.workspace_bytes(3) == 48  # 24 rounded up to 32, plus 16
+    maps = 256 * 8 * 2 * 128  # per-CTA tensor-map copies for wgrad
+    assert _capi.workspace_bytes(0) == 128 + maps
+    assert _capi.workspace_bytes(8) == 128 + maps
+    assert _capi.workspace_bytes(100) == 896 + maps  # 800 + 16 rounded up to 128
     with pytest.raises(RuntimeError):
         _capi.workspace_bytes(_capi.MAX_EXPERTS + 1)
 
