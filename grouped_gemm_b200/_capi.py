@@ -11,7 +11,8 @@ import os
 import torch  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libb200gmm.so")
+# B200GMM_LIBRARY points at another build of the same library (A/B comparisons).
+LIB_PATH = os.environ.get("B200GMM_LIBRARY") or os.path.join(_HERE, "csrc", "libb200gmm.so")
 
 OK = 0
 MAX_EXPERTS = 1024

@@ -44,7 +44,7 @@ struct DeviceInfo {
 
 template <int MODE, int CTAS>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                       __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
+                       const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
                        CUtensorMap* slots) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
@@ -58,7 +58,7 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, c, bs, p, status, slots);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, map_c, c, bs, p, status, slots);
 }
 
 template <int MODE, int CTAS>
@@ -112,9 +112,9 @@ int device_info(DeviceInfo** out) {
   return B200GMM_OK;
 }
 
-// bf16 tensor map with 128-byte swizzle; dims/box innermost first.
+// bf16 tensor map (128-byte swizzle unless told otherwise); dims/box innermost first.
 int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-               const uint32_t* box) {
+               const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return B200GMM_ECUDA;
   cuuint64_t gdim[3];
@@ -130,7 +130,7 @@ int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
   }
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
                         const_cast<void*>(base), gdim, gstride, gbox, estride,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200GMM_OK : B200GMM_ETENSORMAP;
 }
@@ -278,18 +278,28 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
       return rc;
   }
 
+  // Output map for the epilogue's TMA stores: 32 x 32 boxes, 64-byte swizzle.
+  // wgrad's c[z, m, n] is addressed as z*m rows.
+  CUtensorMap map_c;
+  {
+    const uint64_t dc[2] = {N, p.mode == kTN ? Z * D1 : T};
+    const uint32_t bc[2] = {32, 32};
+    if (dc[1] >= (uint64_t(1) << 31)) return B200GMM_ELIMIT;
+    if ((rc = encode_map(&map_c, c, 2, dc, bc, CU_TENSOR_MAP_SWIZZLE_64B)) != 0) return rc;
+  }
+
   __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(c);
   cudaError_t err;
   if (ctas == 2) {
     const int grid = dev->pair_ctas < kMaxCtas ? dev->pair_ctas : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
   } else {
     const int grid = dev->sm_count < kMaxCtas ? dev->sm_count : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, cp, bs_dev, p, device_status, slots);
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();

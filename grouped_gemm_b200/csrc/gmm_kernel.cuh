@@ -8,8 +8,11 @@
 //               TMEM), commits each stage back to the producer and each finished
 //               accumulator to the epilogue; two 256-column accumulators alternate
 //               so the epilogue of tile i overlaps the main loop of tile i+1;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator, round to bf16, store the
-//               rows that exist (ragged last tile of an expert is masked).
+//   warps 2-5   epilogue: tcgen05.ld the accumulator 32 columns at a time (the
+//               next load is in flight while the current one is converted), round
+//               to bf16, stage 32x32 chunks in swizzled shared memory and write
+//               them with TMA tensor stores; a warp whose 32 rows do not all exist
+//               (ragged last tile of an expert) stores its valid rows directly.
 //
 // Two variants, chosen on the host:
 //   CTAS == 1   every CTA owns 128 x 256 output tiles (4 stages of 48 KiB);
@@ -59,6 +62,11 @@ struct Geometry {
   static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB either way
 };
 
+// Epilogue staging: per epilogue warp two buffers of 32 rows x 32 bf16 columns
+// (64-byte rows, 64-byte swizzle), the source of the TMA stores.
+constexpr uint32_t kStageOutBytes = 32 * 32 * 2;            // 2 KiB
+constexpr uint32_t kOutBytes = 4 * 2 * kStageOutBytes;      // 16 KiB
+
 struct __align__(8) SmemTail {
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
@@ -70,7 +78,9 @@ struct __align__(8) SmemTail {
   int tile_start[kMaxExperts + 1];
 };
 
-constexpr size_t kSmemBytes = 1024 /*alignment slack*/ + Geometry<1>::kRingBytes + sizeof(SmemTail);
+constexpr size_t kSmemBytes =
+    1024 /*alignment slack*/ + Geometry<1>::kRingBytes + kOutBytes + sizeof(SmemTail);
+static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 static_assert(Geometry<1>::kRingBytes == Geometry<2>::kRingBytes, "both variants use the same ring size");
 
 // Exclusive prefix sums of batch_sizes (rows) and of per-expert tile counts,
@@ -141,7 +151,8 @@ struct TileWalker {
 template <int MODE, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-           __nv_bfloat16* __restrict__ c, const int64_t* __restrict__ batch_sizes, const Problem p,
+           const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
+           const int64_t* __restrict__ batch_sizes, const Problem p,
            uint32_t* status, CUtensorMap* map_slots) {
   using G = Geometry<CTAS>;
   constexpr int kStages = G::kStages;
@@ -152,7 +163,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   const uint32_t pad = (1024u - (raw_addr & 1023u)) & 1023u;
   uint8_t* smem = smem_raw + pad;  // 1024-byte aligned: required by the 128-byte swizzle
   const uint32_t stage_base = raw_addr + pad;
-  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + G::kRingBytes);
+  const uint32_t out_base = stage_base + G::kRingBytes;
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + G::kRingBytes + kOutBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -165,6 +177,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
+      ptx::prefetch_tensormap(&map_c);
       for (int s = 0; s < kStages; ++s) {
         ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
         ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
@@ -357,17 +370,70 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   } else {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;  // TMEM lane quadrant this warp may read
+    const uint32_t my_out = out_base + uint32_t(q) * 2u * kStageOutBytes;
     TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
     Tile t;
     uint32_t it = 0;
+    uint32_t stores = 0;  // TMA stores this warp has issued (lane 0's bulk groups)
     bool ok = true;
+
+    // One 32-column chunk `v` of this lane's row: either into the staging buffer
+    // and out through a TMA store (whole warp valid), or straight to global.
+    auto emit = [&](const uint32_t (&v)[32], int ch, bool warp_full, bool row_ok,
+                    __nv_bfloat16* crow, int cols_left, int tile_row, int col0) {
+      if (ch * 32 >= cols_left) return;  // chunk lies entirely past the last column
+      uint4 o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 h;
+        h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
+        o[j].x = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
+        o[j].y = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
+        o[j].z = *reinterpret_cast<uint32_t*>(&h);
+        h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
+        o[j].w = *reinterpret_cast<uint32_t*>(&h);
+      }
+      if (warp_full) {
+        const uint32_t buf = my_out + (stores & 1u) * kStageOutBytes;
+        // The store issued two chunks ago read this buffer; it must be done reading.
+        if (lane == 0 && stores >= 2) ptx::bulk_wait_group_read<1>();
+        __syncwarp();
+        // 64-byte swizzle: 16-byte chunk index ^= (row / 2) % 4.
+        const uint32_t row_addr = buf + uint32_t(lane) * 64u;
+        const uint32_t sw = (uint32_t(lane) >> 1) & 3u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint32_t dst = row_addr + ((uint32_t(j) ^ sw) << 4);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[j].x), "r"(o[j].y),
+                       "r"(o[j].z), "r"(o[j].w)
+                       : "memory");
+        }
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          ptx::tma_store_2d(&map_c, buf, col0 + ch * 32, tile_row);
+          ptx::bulk_commit_group();
+        }
+        ++stores;
+      } else if (row_ok) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int col = ch * 32 + j * 8;
+          if (col < cols_left) *reinterpret_cast<uint4*>(crow + col) = o[j];
+        }
+      }
+    };
+
     while (ok && walk.next(&t)) {
       const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
       const int r = row_off + q * 32 + lane;  // row inside the (pair) tile
       const bool row_ok = r < t.valid_rows;
-      const int64_t out_row = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0 + r)
-                                            : (int64_t(t.row0) + r);
-      __nv_bfloat16* crow = c + out_row * p.n + t.col0;
+      const bool warp_full = (row_off + q * 32 + 31) < t.valid_rows;
+      const int64_t out_row0 = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0) : int64_t(t.row0);
+      __nv_bfloat16* crow = c + (out_row0 + r) * p.n + t.col0;
+      const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp
       const int cols_left = static_cast<int>(p.n) - t.col0;  // multiple of 8
       if (nkb == 0) {
         if (row_ok) {
@@ -382,39 +448,32 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[ab]), aph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN;
+      uint32_t va[32], vb[32];
+      ptx::tmem_ld_32x32(taddr, va);
 #pragma unroll 1
-      for (int ch = 0; ch < kBlockN / 32; ++ch) {
-        uint32_t v[32];
-        ptx::tmem_ld_32x32(taddr + ch * 32, v);
+      for (int ch = 0; ch < kBlockN / 32; ch += 2) {
         ptx::tmem_ld_wait();
-        if (row_ok) {
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = ch * 32 + j * 8;
-            if (col < cols_left) {
-              uint4 o;
-              __nv_bfloat162 h;
-              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 0]), __uint_as_float(v[j * 8 + 1]));
-              o.x = *reinterpret_cast<uint32_t*>(&h);
-              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 2]), __uint_as_float(v[j * 8 + 3]));
-              o.y = *reinterpret_cast<uint32_t*>(&h);
-              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 4]), __uint_as_float(v[j * 8 + 5]));
-              o.z = *reinterpret_cast<uint32_t*>(&h);
-              h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
-              o.w = *reinterpret_cast<uint32_t*>(&h);
-              *reinterpret_cast<uint4*>(crow + col) = o;
-            }
+        ptx::tmem_ld_32x32(taddr + (ch + 1) * 32, vb);
+        emit(va, ch, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
+        ptx::tmem_ld_wait();
+        if (ch + 2 < kBlockN / 32) {
+          ptx::tmem_ld_32x32(taddr + (ch + 2) * 32, va);
+        } else {
+          // Every column has been read: hand the accumulator back before the last stores.
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) {
+            const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
+            if (kPair) ptx::mbar_arrive_cluster(ptx::mapa(te_bar, 0));
+            else ptx::mbar_arrive(te_bar);
           }
         }
-      }
-      ptx::tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) {
-        const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
-        if (kPair) ptx::mbar_arrive_cluster(ptx::mapa(te_bar, 0));
-        else ptx::mbar_arrive(te_bar);
+        emit(vb, ch + 1, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
       }
     }
+    // Shared memory must outlive the stores that still read it.
+    if (lane == 0) ptx::bulk_wait_group_all();
+    __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown

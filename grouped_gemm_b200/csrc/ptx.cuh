@@ -112,6 +112,27 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint3
       : "memory");
 }
 
+// ---------------------------------------------------------------- TMA stores
+// shared -> global tile store (bulk async group of the issuing thread).
+__device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               :
+               : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Wait until at most N of this thread's bulk groups still have to READ their source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+// Wait until all of this thread's bulk groups are complete.
+__device__ __forceinline__ void bulk_wait_group_all() {
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- tcgen05
 // Whole-warp instructions (.sync.aligned): call with all 32 lanes converged.
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
