@@ -79,7 +79,7 @@ class ClockSampler:
         0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting",
     }
 
-    def __init__(self, index, period=0.05):
+    def __init__(self, index, period=0.01):
         self.index, self.period = index, period
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -194,23 +194,25 @@ def cpu_step(sizes, a, b, grad):
     return 3 * 2.0 * sum(sizes) * MIXTRAL["k"] * MIXTRAL["n"]
 
 
-def calibrate_cpu(target_s):
-    """Pick the row fraction whose step takes about ``target_s`` seconds."""
+def pick_cpu_sample(target_s):
+    """Inputs of the CPU sample whose step takes about ``target_s`` seconds on
+    this host (at most the full workload).  Small samples run far below the
+    host's large-matrix rate, so the sample is grown until one step is long
+    enough.  Returns (frac, sizes, a, b, grad, seconds of the last step)."""
     frac = 1.0 / 256
-    sizes, a, b, grad = cpu_sample_inputs(frac)
-    cpu_step(sizes, a, b, grad)  # warm-up (thread pool, oneDNN primitives)
-    t0 = time.perf_counter()
-    flops = cpu_step(sizes, a, b, grad)
-    dt = max(time.perf_counter() - t0, 1e-4)
-    rate = flops / dt
-    full = 3 * 2.0 * MIXTRAL["rows"] * MIXTRAL["k"] * MIXTRAL["n"]
-    return min(1.0, max(1.0 / 256, target_s * rate / full))
+    while True:
+        sizes, a, b, grad = cpu_sample_inputs(frac)
+        cpu_step(sizes, a, b, grad)  # warm-up (thread pool, primitive caches)
+        t0 = time.perf_counter()
+        cpu_step(sizes, a, b, grad)
+        dt = max(time.perf_counter() - t0, 1e-3)
+        if dt >= 0.6 * target_s or frac >= 1.0:
+            return frac, sizes, a, b, grad, dt
+        frac = min(1.0, frac * min(8.0, target_s / dt))
 
 
 def cpu_baseline(target_s=12.0):
-    frac = calibrate_cpu(target_s)
-    sizes, a, b, grad = cpu_sample_inputs(frac)
-    cpu_step(sizes, a, b, grad)
+    frac, sizes, a, b, grad, _ = pick_cpu_sample(target_s)
     t0 = time.perf_counter()
     flops = cpu_step(sizes, a, b, grad)
     dt = time.perf_counter() - t0
@@ -230,8 +232,7 @@ def run_reference(args):
     world, rank, _ = dist_info()
     if rank != 0:
         return
-    frac = calibrate_cpu(3.0)
-    sizes, a, b, grad = cpu_sample_inputs(frac)
+    frac, sizes, a, b, grad, _ = pick_cpu_sample(3.0)
     for _ in range(args.warmup):
         cpu_step(sizes, a, b, grad)
     t0 = time.perf_counter()

@@ -1,6 +1,7 @@
 """Build libb200gmm.so in-tree with nvcc for sm_100a.
 
-Usage: ``python -m grouped_gemm_b200.csrc.build [--force] [--verbose]``.
+Usage: ``python grouped_gemm_b200/csrc/build.py [--force] [--verbose]`` (run it
+as a script: importing the package first would try to load the library).
 The library has no torch dependency; it links the shared CUDA runtime so that a
 process that already loaded torch's libcudart shares one runtime with it.
 """
