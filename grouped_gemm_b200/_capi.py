@@ -17,6 +17,7 @@ LIB_PATH = os.environ.get("B200GMM_LIBRARY") or os.path.join(_HERE, "csrc", "lib
 OK = 0
 MAX_EXPERTS = 1024
 FILL_FIELDS = 9
+STATIC_MAX_EXPERTS = 256
 STATUS_TIMEOUT = 0x1
 STATUS_NEGATIVE_SIZE = 0x2
 STATUS_ROWS_OVERFLOW = 0x4
@@ -29,6 +30,10 @@ SIGNATURES = {
         _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
+    "b200gmm_run_static": (_c.c_int, [
+        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
+        _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
+        _c.c_void_p, _c.c_void_p]),
     "b200gmm_fill_offsets": (_c.c_int, [
         _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_void_p]),
@@ -50,10 +55,13 @@ def load():
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} is missing: build it with `python -m grouped_gemm_b200.csrc.build` "
+            f"{LIB_PATH} is missing: build it with `python grouped_gemm_b200/csrc/build.py` "
             "(needs nvcc; there is no non-CUDA fallback)")
     lib = ctypes.CDLL(LIB_PATH)
     for name, (restype, argtypes) in SIGNATURES.items():
+        if not hasattr(lib, name):
+            raise ImportError(f"{LIB_PATH} lacks {name}: it is older than its sources, rebuild it with "
+                              "`python grouped_gemm_b200/csrc/build.py --force`")
         fn = getattr(lib, name)
         fn.restype = restype
         fn.argtypes = argtypes

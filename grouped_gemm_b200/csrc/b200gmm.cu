@@ -178,6 +178,36 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
 
 size_t round128(size_t x) { return (x + 127) & ~size_t(127); }
 
+// ---- scratch for b200gmm_run_static ------------------------------------------
+// Same layout as a caller-provided workspace, sized for the entry point's own
+// expert limit.  Lives in every CUDA context that loads this library, from load
+// until exit.
+constexpr size_t kStaticScratchBytes =
+    ((size_t(B200GMM_STATIC_MAX_EXPERTS) * sizeof(int64_t) + 16 + 127) & ~size_t(127)) +
+    size_t(kMaxCtas) * kMapSlots * 2 * sizeof(CUtensorMap);
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// Device address of g_static_scratch on the current device.  In host code the
+// symbol's name is only a handle; the address a kernel can use has to be asked
+// for, per device, with that device current.
+int static_scratch_address(void** out) {
+  static std::mutex mu;
+  static void* addr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200GMM_ECUDA;
+  std::lock_guard<std::mutex> lock(mu);
+  if (addr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return B200GMM_ECUDA;
+    }
+    addr[dev] = p;
+  }
+  *out = addr[dev];
+  return B200GMM_OK;
+}
+
 // Workspace layout: [0, 8z) device copy of batch_sizes; then, 128-byte aligned,
 // kMaxCtas x kMapSlots x {a, b} tensor maps edited by the wgrad kernel.
 size_t maps_offset(int z) { return round128(size_t(z) * sizeof(int64_t) + 16); }
@@ -307,6 +337,17 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return B200GMM_OK;
+}
+
+int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* batch_sizes,
+                       int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
+                       int trans_a, int trans_b, uint32_t* device_status, void* cuda_stream) {
+  if (z > B200GMM_STATIC_MAX_EXPERTS) return B200GMM_ELIMIT;
+  void* scratch = nullptr;
+  const int rc = static_scratch_address(&scratch);
+  if (rc != B200GMM_OK) return rc;
+  return b200gmm_run(a, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, trans_a,
+                     trans_b, scratch, kStaticScratchBytes, device_status, cuda_stream);
 }
 
 int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a1, int64_t n,

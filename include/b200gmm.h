@@ -41,6 +41,10 @@ extern "C" {
 #define B200GMM_STATUS_NEGATIVE_SIZE 0x2u  /* a batch size was < 0 (treated as 0) */
 #define B200GMM_STATUS_ROWS_OVERFLOW 0x4u  /* sum(batch_sizes) > rows of a (clamped) */
 
+/* Largest number of experts b200gmm_run_static accepts (its built-in scratch is
+ * sized for this many). */
+#define B200GMM_STATIC_MAX_EXPERTS 256
+
 /* Number of int64 fields b200gmm_fill_offsets writes per expert:
  * m, n, k, lda, ldb, ldc, a_offset, b_offset, c_offset (offsets in elements). */
 #define B200GMM_FILL_FIELDS 9
@@ -94,6 +98,39 @@ int b200gmm_run(const void* a, const void* b, void* c,
                 int trans_a, int trans_b,
                 void* workspace, size_t workspace_bytes,
                 uint32_t* device_status, void* cuda_stream);
+
+/*
+ * b200gmm_run for callers that have no device memory to hand over and may not
+ * create any: same arguments, same kernel and same results as b200gmm_run, but
+ * without the workspace pair.  (This entry point has no counterpart in the
+ * reference, which always allocates its scratch through torch.)
+ *
+ * Who needs it: code that runs where allocating is not an option -- an inference
+ * server that has already given all free HBM to its own cache pool, a plugin
+ * that is handed input and output buffers and nothing else, a latency-critical
+ * thread that must not take the allocator's or the driver's locks.  The scratch
+ * (device copy of batch_sizes, per-CTA tensor-map copies) lives in a fixed
+ * array inside the library image, about 0.5 MB, present on every GPU that loads
+ * the library for as long as the process runs.  This function calls no
+ * cudaMalloc / cudaFree and no allocating library routine.
+ *
+ * Limits and rules:
+ *  - at most B200GMM_STATIC_MAX_EXPERTS experts; more returns B200GMM_ELIMIT
+ *    and launches nothing;
+ *  - the first call on each device looks up the array's device address (a few
+ *    CUDA runtime queries with that device current); make that first call
+ *    before starting any stream capture on that device;
+ *  - all calls on one device share the one array.  Nothing in it has to start
+ *    out zeroed (each call overwrites what it reads), but two calls whose
+ *    kernels can overlap on the GPU -- different streams without an ordering
+ *    between them -- race on it.  Keep such calls on one stream or order them
+ *    with events; use b200gmm_run with separate workspaces for concurrency.
+ */
+int b200gmm_run_static(const void* a, const void* b, void* c,
+                       const int64_t* batch_sizes, int batch_sizes_on_device,
+                       int z, int64_t tokens, int64_t dim_a1, int64_t n,
+                       int trans_a, int trans_b,
+                       uint32_t* device_status, void* cuda_stream);
 
 /*
  * Device-side argument fill on its own, for inspection and bit-exact tests:
