@@ -453,6 +453,9 @@ def ep_value_single(args):
 
 
 def run_multi(args):
+    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the JSON line only.
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     import torch.distributed as dist
     from grouped_gemm_b200 import _capi, backend
     world, rank, local = dist_info()

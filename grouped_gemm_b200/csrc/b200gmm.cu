@@ -168,6 +168,7 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   p->tile_m = kBlockM * ctas;
   p->group_m = env_int("B200GMM_GROUP_M", ctas == 2 ? 8 : 16);
   if (p->group_m < 1) p->group_m = 1;
+  p->direct_store = env_int("B200GMM_DIRECT_STORE", 0) != 0;
   // Upper bound on the tile count must fit the kernel's 32-bit tile index.
   const int64_t nt = (n + kBlockN - 1) / kBlockN;
   const int64_t row_tiles = trans_a ? int64_t(z) * ((d1 + p->tile_m - 1) / p->tile_m)
@@ -365,6 +366,7 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a
   p.n = n;
   p.tile_m = kBlockM;
   p.group_m = 1;
+  p.direct_store = 0;
   fill_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(batch_sizes_device, p,
                                                                             out_device);
   if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;

@@ -430,7 +430,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
       const int r = row_off + q * 32 + lane;  // row inside the (pair) tile
       const bool row_ok = r < t.valid_rows;
-      const bool warp_full = (row_off + q * 32 + 31) < t.valid_rows;
+      const bool warp_full = !p.direct_store && (row_off + q * 32 + 31) < t.valid_rows;
       const int64_t out_row0 = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0) : int64_t(t.row0);
       __nv_bfloat16* crow = c + (out_row0 + r) * p.n + t.col0;
       const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp

@@ -36,6 +36,7 @@ struct Problem {
   int64_t n;       // output columns
   int tile_m;      // output rows per scheduled tile: 128 (one CTA) or 256 (a CTA pair)
   int group_m;     // row-tiles swept together across the columns (L2 reuse of b)
+  int direct_store;  // 1: epilogue writes every row with plain stores (no TMA stores)
 };
 
 struct Tile {
