@@ -12,8 +12,10 @@ One JSON line on stdout (rank 0).  Workloads (synthetic, seeded; bf16):
   is forward (a@b) + dgrad (grad@b^T) + wgrad (a^T@grad): three kernel launches.
 * N > 1: expert-parallel projection, z=64 experts sharded evenly, 65536 tokens x
   top-4 = 262144 rows, hidden 6144, ffn 10752, uniform routing seed 3.  A step is
-  dispatch (all-to-all) -> forward -> combine, then dispatch of the output
-  gradient -> dgrad + wgrad -> combine.  Total work is fixed ("strong" scaling).
+  dispatch -> forward -> combine, then dispatch of the output gradient -> dgrad +
+  wgrad -> combine.  Rows move between GPUs with the library's peer-memory push
+  kernel (--exchange nccl: NCCL all-to-all instead).  Total work is fixed
+  ("strong" scaling); the line also carries the same workload timed on one GPU.
 
 ``value`` is TFLOP/s over the timed steps with inputs resident in HBM, timed with
 CUDA events (max over ranks).  ``e2e`` is the same step driven from pinned host
@@ -267,7 +269,7 @@ def workload_config(n_gpus):
                 "l2": "inputs larger than L2 (2.1 GB read per pass, no flush)"}
     return {"workload": f"expert-parallel projection fwd+dgrad+wgrad (BASELINE configs[4]): z=64 sharded over "
                         f"{n_gpus} ranks, 65536 tokens x top-4 = 262144 rows, hidden 6144, ffn 10752, uniform "
-                        "routing seed 3, NCCL all-to-all dispatch/combine",
+                        "routing seed 3, dispatch/combine over NVLink",
             "parallelism": f"ep{n_gpus}",
             "l2": "inputs larger than L2 (per-rank operands of several GB, no flush)"}
 
@@ -344,7 +346,7 @@ def run_single(args):
     # end to end: pinned host buffers in and out, copies inside the timed region
     e2e = e2e_single(backend, a, b, grad, bs, flops_pass, min(args.steps, 3))
 
-    scaling_base = ep_value_single(args) if args.scaling_base else None
+    scaling_base = ep_value_single(args.steps, dev) if args.scaling_base else None
     baseline = cpu_baseline() if not args.no_cpu_baseline else None
 
     line = {
@@ -433,38 +435,75 @@ def ep_flops():
     return 3 * 2.0 * EP["tokens"] * EP["top_k"] * EP["hidden"] * EP["ffn"]
 
 
-def ep_value_single(args):
-    """Config 5 on one GPU (all 64 experts local, no exchange): the denominator
-    for strong-scaling efficiency of the multi-GPU lines."""
-    from grouped_gemm_b200 import backend
-    dev = torch.device("cuda", 0)
-    ep, plan, x, w, grad = ep_setup(1, 0, dev)
+def ep_value_single(steps, dev):
+    """Config 5 on one GPU (all 64 experts local, rows only permuted): the
+    denominator for strong-scaling efficiency of the multi-GPU lines."""
+    from grouped_gemm_b200 import backend, expert_parallel as ep
+    ids = ep_routing(EP["tokens"], EP["z"], EP["top_k"]).to(dev)
+    g = torch.Generator(device=dev).manual_seed(100)
+    x = torch.randn(EP["tokens"], EP["hidden"], device=dev, generator=g).bfloat16()
+    w = (torch.randn(EP["z"], EP["hidden"], EP["ffn"], device=dev, generator=g) * 0.02).bfloat16()
+    grad = torch.randn(EP["tokens"] * EP["top_k"], EP["ffn"], device=dev, generator=g).bfloat16()
+    px = ep.PeerExchange(ids, EP["z"], EP["hidden"], EP["ffn"], single_rank=True)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
-    step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+    step = lambda: px.step(x, w, grad, gmm_fn)
     for _ in range(2):
         step()
-    steps = max(2, min(args.steps, 5))
-    ms = timed_region(step, steps, 1) / steps
+    steps = max(2, min(steps, 5))
+    ms = time_loop(step, steps)
     out = {"workload": workload_config(2)["workload"].replace("over 2 ranks", "over 1 rank"),
            "value": ep_flops() / ms / 1e9, "unit": UNIT, "ms_per_step": ms, "steps": steps}
-    del x, w, grad, plan
+    del x, w, grad, px
     torch.cuda.empty_cache()
     return out
 
 
+class StdoutToStderr:
+    """Send file descriptor 1 to stderr while libraries initialise (NCCL prints
+    its version banner on stdout), so that stdout carries the JSON line only."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        os.dup2(2, 1)
+        return self
+
+    def __exit__(self, *exc):
+        sys.stdout.flush()
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+
+
 def run_multi(args):
-    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the JSON line only.
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"
+    with StdoutToStderr():
+        line = measure_multi(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def measure_multi(args):
     import torch.distributed as dist
     from grouped_gemm_b200 import _capi, backend
     world, rank, local = dist_info()
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", device_id=dev)
+    # Same workload on one GPU first (rank 0 alone; the others wait): the
+    # denominator a reader needs for strong-scaling efficiency.
+    scaling_base = None
+    if rank == 0 and not args.no_scaling_base:
+        scaling_base = ep_value_single(args.steps, dev)
+    dist.barrier()
     ep, plan, x, w, grad = ep_setup(world, rank, dev)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
-    step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+    if args.exchange == "peer":
+        per = EP["tokens"] // world
+        px = ep.PeerExchange(ep_routing()[rank * per:(rank + 1) * per].to(dev), EP["z"], EP["hidden"], EP["ffn"])
+        step = lambda: px.step(x, w, grad, gmm_fn)
+        exchange_step = step
+    else:
+        step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+        exchange_step = step
     for _ in range(max(args.warmup, 3)):
         step()
     launches0 = _capi.launch_count()
@@ -497,7 +536,7 @@ def run_multi(args):
     def e2e_step():
         x.copy_(hx, non_blocking=True)
         grad.copy_(hg, non_blocking=True)
-        out_rows, dx, dw = ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+        out_rows, dx, dw = exchange_step()
         ho.copy_(out_rows, non_blocking=True)
         hdx.copy_(dx, non_blocking=True)
         hdw.copy_(dw, non_blocking=True)
@@ -508,6 +547,7 @@ def run_multi(args):
     peaks = measured_peaks()
     status = torch.tensor([backend.device_status(dev)], device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    line = None
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
@@ -518,15 +558,18 @@ def run_multi(args):
                          "achieved": ep_flops() / world / ms_gemm / 1e9, "peak": peaks["sustained"],
                          "unit": "TFLOP/s", "frac": ep_flops() / world / ms_gemm / 1e9 / peaks["sustained"],
                          "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (per GPU)", "traffic": None},
+            "exchange": ("peer memory: b200gmm_push_rows over NVLink (symmetric memory), 4 pushes + 4 barriers per step"
+                         if args.exchange == "peer" else "NCCL all_to_all_single + index gathers"),
             "exchange_share": 1.0 - ms_gemm / ms_step, "ms_gemm_per_step": ms_gemm,
+            "scaling_base": scaling_base,
             "cpu_baseline": None,
             "e2e": {"value": ep_flops() / ms_e2e / 1e9, "unit": UNIT, "ms_per_step": ms_e2e,
                     "h2d_bytes_per_step": (hx.numel() + hg.numel()) * 2 * world,
                     "d2h_bytes_per_step": (ho.numel() + hdx.numel() + hdw.numel()) * 2 * world},
             "gpu_launches": launches, "clocks": clocks.summary(), "device_status": int(status.item()),
         }
-        print(json.dumps(line), flush=True)
     dist.destroy_process_group()
+    return line
 
 
 def run_profile_case(args):
@@ -570,6 +613,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
+                    help="multi-GPU row exchange: peer-memory pushes (default) or NCCL all-to-all")
+    ap.add_argument("--no-scaling-base", action="store_true",
+                    help="multi-GPU runs: skip timing the same workload on rank 0's GPU alone")
     ap.add_argument("--scaling-base", action="store_true",
                     help="also time the multi-GPU workload on this one GPU (strong-scaling denominator)")
     args = ap.parse_args()

@@ -34,6 +34,9 @@ SIGNATURES = {
         _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_void_p]),
+    "b200gmm_push_rows": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+        _c.c_void_p]),
     "b200gmm_fill_offsets": (_c.c_int, [
         _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_void_p]),

@@ -10,6 +10,7 @@
 #include <cstdlib>
 #include <mutex>
 
+#include "ep_exchange.cuh"
 #include "gmm_kernel.cuh"
 
 namespace {
@@ -349,6 +350,29 @@ int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* bat
   if (rc != B200GMM_OK) return rc;
   return b200gmm_run(a, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, trans_a,
                      trans_b, scratch, kStaticScratchBytes, device_status, cuda_stream);
+}
+
+int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items, const int32_t* src_row,
+                      const int32_t* dst_rank, const int64_t* dst_row, const void* const* peer_base,
+                      void* cuda_stream) {
+  if (row_bytes <= 0 || (row_bytes % 16) != 0 || n_items < 0) return B200GMM_EINVAL;
+  if (n_items == 0) return B200GMM_OK;
+  if (src == nullptr || dst_rank == nullptr || dst_row == nullptr || peer_base == nullptr)
+    return B200GMM_EINVAL;
+  if (reinterpret_cast<uintptr_t>(src) & 15) return B200GMM_EALIGN;
+  DeviceInfo* dev = nullptr;
+  const int rc = device_info(&dev);
+  if (rc != B200GMM_OK) return rc;
+  // Enough CTAs to keep every SM's load/store pipes busy; rows are handed out
+  // grid-stride.
+  int64_t grid = int64_t(dev->sm_count) * 8;
+  if (grid > n_items) grid = n_items;
+  push_rows_kernel<<<static_cast<unsigned>(grid), kPushThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint4*>(src), row_bytes / 16, n_items, src_row, dst_rank, dst_row,
+      const_cast<void* const*>(peer_base));
+  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200GMM_OK;
 }
 
 int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a1, int64_t n,

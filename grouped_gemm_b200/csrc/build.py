@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
 SOURCES = ["b200gmm.cu"]
-HEADERS = ["gmm_kernel.cuh", "ptx.cuh", "schedule.cuh", os.path.join(ROOT, "include", "b200gmm.h")]
+HEADERS = ["gmm_kernel.cuh", "ptx.cuh", "schedule.cuh", "ep_exchange.cuh", os.path.join(ROOT, "include", "b200gmm.h")]
 LIB = os.path.join(HERE, "libb200gmm.so")
 
 

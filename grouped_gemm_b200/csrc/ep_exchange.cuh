@@ -1,0 +1,48 @@
+// Row exchange for expert parallelism over peer memory.
+//
+// One kernel moves token rows between GPUs: every item is one row that is read
+// from this GPU's memory and written, with plain 16-byte stores, to a row of a
+// buffer on the GPU that needs it (possibly this one).  The destination
+// buffers are symmetric-memory allocations mapped into this process, so the
+// stores travel over NVLink / NVSwitch without a staging copy, a packing pass or
+// a collective.  No TMA and no multicast is involved; remote memory is only
+// ever the target of ordinary stores.
+//
+// The reference (tgale96/grouped_gemm) has no multi-GPU code; callers sort rows
+// by expert before gmm and un-sort after.  This kernel is that permutation and
+// the inter-GPU transfer in one pass.
+#pragma once
+
+#include <stdint.h>
+
+namespace b200gmm {
+
+constexpr int kPushThreads = 256;
+
+// item i: row src_row[i] (or i when src_row == nullptr) of `src`
+//      -> row dst_row[i] of the buffer peer_base[dst_rank[i]].
+__global__ void __launch_bounds__(kPushThreads)
+push_rows_kernel(const uint4* __restrict__ src, int64_t row_vecs, int64_t n_items,
+                 const int32_t* __restrict__ src_row, const int32_t* __restrict__ dst_rank,
+                 const int64_t* __restrict__ dst_row, void* const* __restrict__ peer_base) {
+  for (int64_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+    const int64_t sr = (src_row != nullptr) ? src_row[item] : item;
+    const uint4* s = src + sr * row_vecs;
+    uint4* d = static_cast<uint4*>(peer_base[dst_rank[item]]) + dst_row[item] * row_vecs;
+    int64_t v = threadIdx.x;
+    // four independent 16-byte loads in flight per thread before the stores
+    for (; v + 3 * kPushThreads < row_vecs; v += 4 * kPushThreads) {
+      const uint4 r0 = __ldg(s + v);
+      const uint4 r1 = __ldg(s + v + kPushThreads);
+      const uint4 r2 = __ldg(s + v + 2 * kPushThreads);
+      const uint4 r3 = __ldg(s + v + 3 * kPushThreads);
+      d[v] = r0;
+      d[v + kPushThreads] = r1;
+      d[v + 2 * kPushThreads] = r2;
+      d[v + 3 * kPushThreads] = r3;
+    }
+    for (; v < row_vecs; v += kPushThreads) d[v] = __ldg(s + v);
+  }
+}
+
+}  // namespace b200gmm

@@ -146,3 +146,184 @@ def expert_parallel_step(x, w, grad_rows, plan, gmm_fn, group=None):
     dw = gmm_fn(a, g, plan.batch_sizes, True, False)
     dx = combine(da, plan, group, reduce=True)
     return out_rows, dx, dw
+
+
+# ---------------------------------------------------------------------------
+# Peer-memory exchange: one pass per exchange instead of gather + all-to-all +
+# regroup.  Each rank writes its rows straight into the expert-grouped buffer
+# of the rank that owns the expert (and, on the way back, straight into the
+# token owner's slot-ordered buffer) with ``b200gmm_push_rows`` over NVLink.
+# ---------------------------------------------------------------------------
+class PeerExchange:
+    """Plan + symmetric buffers for one routing.
+
+    Buffers (all in one symmetric allocation per rank, same size on every rank):
+      ``a_grouped``  [cap, h_in]   dispatch target, rows grouped by local expert
+      ``g_grouped``  [cap, h_out]  dispatch target for output gradients
+      ``out_slots``  [pairs, h_out] combine target, (token, slot) order
+      ``da_slots``   [pairs, h_in]  combine target for dgrad rows
+    ``cap`` is the largest number of rows any rank receives, ``pairs`` the largest
+    tokens*top_k of any rank.  Rows of expert e on its owner are ordered by source
+    rank, then by the source's (token, slot) order: the same layout the
+    all-to-all path produces.
+    """
+
+    def __init__(self, expert_ids, num_experts, h_in, h_out, group=None, dtype=torch.bfloat16,
+                 single_rank=False):
+        from grouped_gemm_b200 import _capi
+
+        self._lib = _capi.load()
+        self._check = _capi.check
+        # single_rank: every expert is local to this process (also the mode used
+        # when torch.distributed is not initialised); buffers are ordinary tensors.
+        single_rank = single_rank or not dist.is_initialized()
+        if not single_rank:
+            self.group = group if group is not None else dist.group.WORLD
+            self.world = dist.get_world_size(self.group)
+            self.rank = dist.get_rank(self.group)
+        else:
+            self.group, self.world, self.rank = None, 1, 0
+        assert num_experts % self.world == 0, "experts must divide evenly across ranks"
+        self.per_rank = num_experts // self.world
+        self.num_tokens, self.top_k = expert_ids.shape
+        self.h_in, self.h_out, self.dtype = h_in, h_out, dtype
+        device = expert_ids.device
+        self.device = device
+        esize = torch.empty(0, dtype=dtype).element_size()
+        assert (h_in * esize) % 16 == 0 and (h_out * esize) % 16 == 0
+
+        flat = expert_ids.reshape(-1)
+        counts = torch.bincount(flat, minlength=num_experts)
+        all_counts = torch.empty(self.world, num_experts, dtype=counts.dtype, device=device)
+        if self.world > 1:
+            dist.all_gather_into_tensor(all_counts, counts.contiguous(), group=self.group)
+        else:
+            all_counts[0] = counts
+        C = all_counts.cpu()                                   # [source rank, global expert]
+        per_expert = C.sum(0)                                  # rows of each expert, all sources
+        owner = torch.arange(num_experts) // self.per_rank
+        # first row of expert e inside its owner's buffer, then of source s inside e
+        expert_base = torch.zeros(num_experts, dtype=torch.int64)
+        for d in range(self.world):
+            sl = slice(d * self.per_rank, (d + 1) * self.per_rank)
+            expert_base[sl] = torch.cumsum(per_expert[sl], 0) - per_expert[sl]
+        before_me = C[: self.rank].sum(0) if self.rank > 0 else torch.zeros(num_experts, dtype=torch.int64)
+        my_offset = (expert_base + before_me).to(device)       # where this rank's rows of expert e start
+        rows_per_rank = [int(per_expert[d * self.per_rank:(d + 1) * self.per_rank].sum()) for d in range(self.world)]
+        self.local_rows = rows_per_rank[self.rank]
+        self.cap = max(max(rows_per_rank), 1)
+        pairs = torch.tensor([self.num_tokens * self.top_k], device=device)
+        if self.world > 1:
+            dist.all_reduce(pairs, op=dist.ReduceOp.MAX, group=self.group)
+        self.pairs_cap = int(pairs.item())
+        self.batch_sizes_host = [int(v) for v in per_expert[self.rank * self.per_rank:(self.rank + 1) * self.per_rank]]
+        self.batch_sizes = torch.tensor(self.batch_sizes_host, dtype=torch.int64, device=device)
+
+        # items in expert-sorted order (stable: (token, slot) order inside an expert)
+        order = torch.argsort(flat, stable=True)
+        e_sorted = flat[order]
+        my_start = (torch.cumsum(counts, 0) - counts)          # start of expert e among this rank's sorted items
+        within = torch.arange(order.numel(), device=device) - my_start[e_sorted]
+        self.item_pair = order.to(torch.int32)                                 # (token*top_k + slot) of each item
+        self.item_token = torch.div(order, self.top_k, rounding_mode="floor").to(torch.int32)
+        self.item_rank = (e_sorted // self.per_rank).to(torch.int32)           # owner of the item's expert
+        self.item_row = (my_offset[e_sorted] + within).to(torch.int64)         # row in the owner's grouped buffer
+        self.n_items = int(order.numel())
+
+        # one symmetric allocation, carved into the four buffers + the origin table
+        def align(n):
+            return (n + 255) // 256 * 256
+        sizes = [self.cap * h_in * esize, self.cap * h_out * esize, self.pairs_cap * h_out * esize,
+                 self.pairs_cap * h_in * esize, self.cap * 16]
+        offs, total = [], 0
+        for n in sizes:
+            offs.append(total)
+            total += align(n)
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self._symm = symm_mem.empty(total, dtype=torch.uint8, device=device)
+            self._hdl = symm_mem.rendezvous(self._symm, self.group)
+            bases = [int(p) for p in self._hdl.buffer_ptrs]
+        else:
+            self._symm = torch.empty(total, dtype=torch.uint8, device=device)
+            self._hdl = None
+            bases = [self._symm.data_ptr()]
+
+        def table(off):
+            return torch.tensor([b + off for b in bases], dtype=torch.int64, device=device)
+
+        def view(off, rows, cols, dt):
+            n = rows * cols * torch.empty(0, dtype=dt).element_size()
+            return self._symm[off:off + n].view(dt).view(rows, cols)
+
+        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin = (table(o) for o in offs)
+        self.a_grouped = view(offs[0], self.cap, h_in, dtype)
+        self.g_grouped = view(offs[1], self.cap, h_out, dtype)
+        self.out_slots = view(offs[2], self.pairs_cap, h_out, dtype)
+        self.da_slots = view(offs[3], self.pairs_cap, h_in, dtype)
+        origin = view(offs[4], self.cap, 4, torch.int32)
+
+        # Tell each owner where its rows came from: push (source rank, pair) records
+        # along the dispatch route once; the way back reuses them.
+        rec = torch.zeros(self.n_items, 4, dtype=torch.int32, device=device)
+        rec[:, 0] = self.rank
+        rec[:, 1] = self.item_pair
+        self.barrier()
+        self._push(rec, None, self.item_rank, self.item_row, self._t_origin)
+        self.barrier()
+        self.back_rank = origin[: self.local_rows, 0].contiguous()
+        self.back_row = origin[: self.local_rows, 1].to(torch.int64).contiguous()
+        self._flag = torch.zeros(1, device=device)
+
+    # -- plumbing ---------------------------------------------------------------
+    def barrier(self):
+        """Every rank's earlier work on the current stream is complete, and visible
+        to its peers, before any rank's later work starts (stream-ordered)."""
+        if self.world > 1:
+            self._hdl.barrier()
+
+    def _push(self, src, src_row, dst_rank, dst_row, table):
+        n_items = int(dst_rank.numel())
+        row_bytes = src.shape[1] * src.element_size()
+        rc = self._lib.b200gmm_push_rows(
+            src.data_ptr(), row_bytes, n_items, 0 if src_row is None else src_row.data_ptr(),
+            dst_rank.data_ptr(), dst_row.data_ptr(), table.data_ptr(),
+            torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "b200gmm_push_rows")
+
+    # -- exchanges --------------------------------------------------------------
+    def dispatch(self, x):
+        """[tokens, h_in] -> this rank's grouped rows [local_rows, h_in]."""
+        self._push(x, self.item_token, self.item_rank, self.item_row, self._t_a)
+        self.barrier()
+        return self.a_grouped[: self.local_rows]
+
+    def dispatch_rows(self, rows):
+        """[tokens*top_k, h_out] per-slot rows -> grouped rows [local_rows, h_out]."""
+        self._push(rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
+        self.barrier()
+        return self.g_grouped[: self.local_rows]
+
+    def combine_rows(self, y):
+        """Grouped rows [local_rows, h_out] -> per-slot rows on the token owners."""
+        self._push(y, None, self.back_rank, self.back_row, self._t_out)
+        self.barrier()
+        return self.out_slots[: self.num_tokens * self.top_k]
+
+    def combine_reduce(self, y):
+        """Grouped rows [local_rows, h_in] -> [tokens, h_in], summed over a token's slots."""
+        self._push(y, None, self.back_rank, self.back_row, self._t_da)
+        self.barrier()
+        slots = self.da_slots[: self.num_tokens * self.top_k]
+        return slots.view(self.num_tokens, self.top_k, self.h_in).sum(1)
+
+    def step(self, x, w, grad_rows, gmm_fn):
+        """Same unit of work as ``expert_parallel_step``, over peer memory."""
+        a = self.dispatch(x)
+        c = gmm_fn(a, w, self.batch_sizes, False, False)
+        out_rows = self.combine_rows(c)
+        g = self.dispatch_rows(grad_rows)
+        da = gmm_fn(g, w, self.batch_sizes, False, True)
+        dw = gmm_fn(a, g, self.batch_sizes, True, False)
+        dx = self.combine_reduce(da)
+        return out_rows, dx, dw

@@ -133,6 +133,25 @@ int b200gmm_run_static(const void* a, const void* b, void* c,
                        uint32_t* device_status, void* cuda_stream);
 
 /*
+ * Row exchange for expert parallelism: copy `n_items` rows of `row_bytes` bytes
+ * (a multiple of 16) from `src` on this GPU into rows of buffers that may live
+ * on other GPUs.  Item i reads row src_row[i] of `src` (row i when src_row is
+ * NULL) and writes row dst_row[i] of the buffer whose base address is
+ * peer_base[dst_rank[i]].  All index arrays and the `peer_base` table are
+ * device memory; the table holds addresses of peer buffers mapped into this
+ * process (symmetric memory or CUDA IPC) and of this GPU's own buffer at its
+ * own rank.  Plain loads and stores only: no TMA, no multicast, and remote
+ * memory is only written, never read.  The caller orders the transfer against
+ * the consumers on the other GPUs (a barrier after the push).
+ * The reference has no counterpart: it is single-GPU and leaves the
+ * sort-by-expert permutation to its callers.
+ */
+int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items,
+                      const int32_t* src_row, const int32_t* dst_rank,
+                      const int64_t* dst_row, const void* const* peer_base,
+                      void* cuda_stream);
+
+/*
  * Device-side argument fill on its own, for inspection and bit-exact tests:
  * runs the same warp-scan the GEMM kernel runs in its prologue and writes
  * z x B200GMM_FILL_FIELDS int64 values (expert-major) to `out_device`.
