@@ -105,6 +105,12 @@ int device_info(DeviceInfo** out) {
       (void)cudaGetLastError();
       clusters = 0;
     }
+    // The row-push kernel uses no shared memory, but it asks for the same
+    // (maximum) shared-memory carveout as the GEMM kernels: an SM changes its
+    // carveout only when idle, so with the default carveout a GEMM CTA could not
+    // become resident next to push CTAs that were launched first.
+    (void)cudaFuncSetAttribute(push_rows_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                               cudaSharedmemCarveoutMaxShared);
     d.pair_ctas = 2 * clusters;
     if (d.pair_ctas > (d.sm_count & ~1)) d.pair_ctas = d.sm_count & ~1;
     d.attrs_set = true;
@@ -363,9 +369,12 @@ int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items, const
   DeviceInfo* dev = nullptr;
   const int rc = device_info(&dev);
   if (rc != B200GMM_OK) return rc;
-  // Enough CTAs to keep every SM's load/store pipes busy; rows are handed out
-  // grid-stride.
-  int64_t grid = int64_t(dev->sm_count) * 8;
+  // Rows are handed out grid-stride to 4 CTAs per SM: enough loads in flight to
+  // fill NVLink and HBM, while leaving thread slots free so that a GEMM kernel
+  // launched on another stream can become resident next to this one (8 CTAs of
+  // 256 threads would fill an SM's 2048 thread slots and lock the GEMM out until
+  // the whole transfer is done).
+  int64_t grid = int64_t(dev->sm_count) * 4;
   if (grid > n_items) grid = n_items;
   push_rows_kernel<<<static_cast<unsigned>(grid), kPushThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint4*>(src), row_bytes / 16, n_items, src_row, dst_rank, dst_row,

@@ -273,7 +273,7 @@ class PeerExchange:
         self.barrier()
         self.back_rank = origin[: self.local_rows, 0].contiguous()
         self.back_row = origin[: self.local_rows, 1].to(torch.int64).contiguous()
-        self._flag = torch.zeros(1, device=device)
+        self.comm_stream = torch.cuda.Stream(device=device)
 
     # -- plumbing ---------------------------------------------------------------
     def barrier(self):
@@ -327,3 +327,50 @@ class PeerExchange:
         dw = gmm_fn(a, g, self.batch_sizes, True, False)
         dx = self.combine_reduce(da)
         return out_rows, dx, dw
+
+    def step_overlapped(self, x, w, grad_rows, gmm_fn):
+        """``step`` with the exchanges on a second stream, hidden behind the GEMMs:
+        the gradient dispatch runs under the forward GEMM, the forward combine
+        under dgrad, the dgrad combine under wgrad.  Only the first dispatch and
+        the tail of the last combine stay exposed.  All cross-rank barriers are
+        issued on the exchange stream, in the same order on every rank; a buffer
+        is overwritten only after a barrier that follows every rank's last read.
+        Same results as ``step``."""
+        compute = torch.cuda.current_stream(self.device)
+        comm = self.comm_stream
+        rows = self.local_rows
+        start = compute.record_event()
+        with torch.cuda.stream(comm):
+            comm.wait_event(start)          # previous consumers of the buffers on this rank
+            self.barrier()                  # ... and on every other rank
+            self._push(x, self.item_token, self.item_rank, self.item_row, self._t_a)
+            self.barrier()
+            a_ready = comm.record_event()
+            self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
+            self.barrier()
+            g_ready = comm.record_event()
+        a = self.a_grouped[:rows]
+        g = self.g_grouped[:rows]
+        compute.wait_event(a_ready)
+        c = gmm_fn(a, w, self.batch_sizes, False, False)
+        c_done = compute.record_event()
+        with torch.cuda.stream(comm):
+            comm.wait_event(c_done)
+            self._push(c, None, self.back_rank, self.back_row, self._t_out)
+            self.barrier()
+            c.record_stream(comm)
+        compute.wait_event(g_ready)
+        da = gmm_fn(g, w, self.batch_sizes, False, True)
+        da_done = compute.record_event()
+        with torch.cuda.stream(comm):
+            comm.wait_event(da_done)
+            self._push(da, None, self.back_rank, self.back_row, self._t_da)
+            self.barrier()
+            da.record_stream(comm)
+            slots = self.da_slots[: self.num_tokens * self.top_k]
+            dx = slots.view(self.num_tokens, self.top_k, self.h_in).sum(1)
+            finished = comm.record_event()
+        dw = gmm_fn(a, g, self.batch_sizes, True, False)
+        compute.wait_event(finished)
+        dx.record_stream(compute)
+        return self.out_slots[: self.num_tokens * self.top_k], dx, dw

@@ -85,6 +85,10 @@ def test_peer_exchange_single_rank_matches_oracle():
     back = px.combine_rows(px.dispatch_rows(grad.cuda()).clone())
     assert torch.equal(back.cpu(), grad)
     out_rows, dx, dw = px.step(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
+    out_rows, dx, dw = out_rows.clone(), dx.clone(), dw.clone()
+    o2, dx2, dw2 = px.step_overlapped(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
+    torch.cuda.synchronize()
+    assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw)
     want_rows, want_dx, want_dw = _unsharded_oracle()
     assert _close(out_rows, want_rows) and _close(dx, want_dx, 5e-2) and _close(dw, want_dw, 5e-2)
     assert bool((dw[Z - 1] == 0).all())
@@ -114,8 +118,12 @@ def _worker(rank, world, port, results):
         o1, dx1, dw1 = ep.expert_parallel_step(xl, wl, gl, plan, gmm_fn)
         px = ep.PeerExchange(il, Z, H_IN, H_OUT)
         o2, dx2, dw2 = px.step(xl, wl, gl, gmm_fn)
+        o2, dx2, dw2 = o2.clone(), dx2.clone(), dw2.clone()
+        for _ in range(3):   # replayed steps reuse the buffers: the barriers must order them
+            o3, dx3, dw3 = px.step_overlapped(xl, wl, gl, gmm_fn)
         torch.cuda.synchronize()
-        same = bool(torch.equal(o1, o2) and torch.equal(dw1, dw2) and torch.equal(dx1, dx2))
+        same = bool(torch.equal(o1, o2) and torch.equal(dw1, dw2) and torch.equal(dx1, dx2)
+                    and torch.equal(o3, o2) and torch.equal(dw3, dw2) and torch.equal(dx3, dx2))
         results[rank] = (same, o2.cpu(), dx2.float().cpu(), dw2.cpu(), backend.device_status(dev))
     finally:
         dist.destroy_process_group()
