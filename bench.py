@@ -363,8 +363,13 @@ def run_single(args):
 
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch at the
-# benchmark's size, from the ncu captures summarised under profiles/.
-TRAFFIC_BYTES = {}
+# benchmark's size, from the ncu captures summarised in
+# profiles/gmm_kernel_mixtral_ncu_full.md (full-size launches, so no scaling).
+TRAFFIC_BYTES = {
+    "gmm_kernel<NN>": 4.405e9 + 0.928e9,
+    "gmm_kernel<NT>": 9.187e9 + 0.267e9,
+    "gmm_kernel<TN>": 6.635e9 + 0.911e9,
+}
 
 
 def fine_grained_hbm(backend, dev, peaks):
