@@ -340,10 +340,19 @@ def run_single(args):
         "algorithmic_bytes": 2.0 * (rows * k + z * k * n + rows * n),
     }
 
-    # small-M, HBM-bound group shapes (BASELINE config 4, forward): report GB/s
+    # BASELINE config 3 also names the down-projection, b [8, 14336, 4096]
+    down = down_projection(backend, dev, bs, iters)
+
+    # small-M, HBM-bound group shapes (BASELINE config 4): report GB/s
+    del a, b, grad
+    torch.cuda.empty_cache()
     hbm = fine_grained_hbm(backend, dev, peaks)
 
     # end to end: pinned host buffers in and out, copies inside the timed region
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+    b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    grad = torch.randn(rows, n, device=dev, generator=g).bfloat16()
     e2e = e2e_single(backend, a, b, grad, bs, flops_pass, min(args.steps, 3))
 
     scaling_base = ep_value_single(args.steps, dev) if args.scaling_base else None
@@ -353,7 +362,8 @@ def run_single(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(1),
-        "passes": passes, "roofline": roofline, "hbm_bound_case": hbm, "cpu_baseline": baseline,
+        "passes": passes, "down_projection": down, "roofline": roofline, "hbm_bound_case": hbm,
+        "cpu_baseline": baseline,
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
         "frac_of_nominal_2250": value / 2250.0, "device_status": backend.device_status(),
     }
@@ -372,27 +382,52 @@ TRAFFIC_BYTES = {
 }
 
 
+def down_projection(backend, dev, bs, iters):
+    """The three passes on the down-projection shapes (k=14336, n=4096)."""
+    z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["n"], MIXTRAL["k"]
+    g = torch.Generator(device=dev).manual_seed(4)
+    a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+    b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    grad = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+    flops = 2.0 * rows * k * n
+    out = {"workload": "b [8, 14336, 4096], a [32768, 14336], same batch sizes"}
+    for name, fn in (("fwd", lambda: backend.gmm(a, b, bs)),
+                     ("dgrad", lambda: backend.gmm(grad, b, bs, trans_b=True)),
+                     ("wgrad", lambda: backend.gmm(a, grad, bs, trans_a=True))):
+        fn()
+        ms = time_loop(fn, iters)
+        out[name] = {"ms": ms, "tflops": flops / ms / 1e9}
+    return out
+
+
 def fine_grained_hbm(backend, dev, peaks):
-    """Forward of BASELINE config 4 (z=256, k=7168, n=2048, 65536 rows, ~20 %
-    empty experts): most groups have < 128 rows, so the weights dominate the
-    traffic and the HBM roofline is the bound.  Algorithmic bytes: a + weights of
-    non-empty experts + c."""
+    """BASELINE config 4 (z=256, k=7168, n=2048, 65536 rows, ~20 % empty experts;
+    median group 59 rows): the weights (forward, dgrad) or the per-expert outputs
+    (wgrad) dominate the traffic, so these passes are judged against the HBM
+    roofline.  Algorithmic bytes: operands + weights of non-empty experts +
+    output; wgrad writes all 256 output blocks."""
     sizes = fine_grained_batch_sizes()
     z, k, n, rows = 256, 7168, 2048, 65536
     g = torch.Generator(device=dev).manual_seed(2)
     a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
     b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    grad = torch.randn(rows, n, device=dev, generator=g).bfloat16()
     bs = torch.tensor(sizes, dtype=torch.int64, device=dev)
-    fn = lambda: backend.gmm(a, b, bs)
-    for _ in range(3):
-        fn()
-    ms = time_loop(fn, 10)
     nonempty = sum(1 for s in sizes if s > 0)
-    nbytes = 2.0 * (rows * k + nonempty * k * n + rows * n)
     flops = 2.0 * rows * k * n
-    return {"workload": "config 4 forward: z=256 k=7168 n=2048 rows=65536, 51 empty experts, median 59 rows",
-            "ms": ms, "gbs": nbytes / ms / 1e6, "hbm_frac": nbytes / ms / 1e6 / peaks["hbm_gbs"],
-            "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes}
+    nbytes = {"fwd": 2.0 * (rows * k + nonempty * k * n + rows * n),
+              "dgrad": 2.0 * (rows * n + nonempty * k * n + rows * k),
+              "wgrad": 2.0 * (rows * k + rows * n + z * k * n)}
+    out = {"workload": "config 4: z=256 k=7168 n=2048 rows=65536, 51 empty experts, median 59 rows"}
+    for name, fn in (("fwd", lambda: backend.gmm(a, b, bs)),
+                     ("dgrad", lambda: backend.gmm(grad, b, bs, trans_b=True)),
+                     ("wgrad", lambda: backend.gmm(a, grad, bs, trans_a=True))):
+        for _ in range(3):
+            fn()
+        ms = time_loop(fn, 10)
+        out[name] = {"ms": ms, "gbs": nbytes[name] / ms / 1e6, "hbm_frac": nbytes[name] / ms / 1e6 / peaks["hbm_gbs"],
+                     "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes[name]}
+    return out
 
 
 def e2e_single(backend, a, b, grad, bs, flops_pass, steps):

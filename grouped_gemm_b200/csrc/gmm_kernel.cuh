@@ -8,11 +8,13 @@
 //               TMEM), commits each stage back to the producer and each finished
 //               accumulator to the epilogue; two 256-column accumulators alternate
 //               so the epilogue of tile i overlaps the main loop of tile i+1;
-//   warps 2-5   epilogue: tcgen05.ld the accumulator 32 columns at a time (the
-//               next load is in flight while the current one is converted), round
-//               to bf16, stage 32x32 chunks in swizzled shared memory and write
-//               them with TMA tensor stores; a warp whose 32 rows do not all exist
-//               (ragged last tile of an expert) stores its valid rows directly.
+//   warps 2-9   epilogue: each warp owns 32 rows x 128 columns of the tile (TMEM
+//               lane quadrant = warp % 4, column half = (warp - 2) / 4).  It
+//               tcgen05.ld's 32 columns at a time (the next load is in flight while
+//               the current one is converted), rounds to bf16, stages the 32x32
+//               chunk in swizzled shared memory and writes it with a TMA tensor
+//               store; a warp whose 32 rows do not all exist (ragged last tile of
+//               an expert) stores its valid rows directly.
 //
 // Two variants, chosen on the host:
 //   CTAS == 1   every CTA owns 128 x 256 output tiles (4 stages of 48 KiB);
@@ -38,7 +40,8 @@
 
 namespace b200gmm {
 
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 32 * (2 + kEpilogueWarps);  // 320
 constexpr int kMaxExperts = 1024;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 6;
@@ -62,10 +65,11 @@ struct Geometry {
   static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB either way
 };
 
-// Epilogue staging: per epilogue warp two buffers of 32 rows x 32 bf16 columns
-// (64-byte rows, 64-byte swizzle), the source of the TMA stores.
-constexpr uint32_t kStageOutBytes = 32 * 32 * 2;            // 2 KiB
-constexpr uint32_t kOutBytes = 4 * 2 * kStageOutBytes;      // 16 KiB
+// Epilogue staging: per epilogue warp one buffer of 32 rows x 32 bf16 columns
+// (64-byte rows, 64-byte swizzle), the source of its TMA stores.  A warp converts
+// its next chunk in registers while the previous store still reads the buffer.
+constexpr uint32_t kStageOutBytes = 32 * 32 * 2;                  // 2 KiB
+constexpr uint32_t kOutBytes = kEpilogueWarps * kStageOutBytes;   // 16 KiB
 
 struct __align__(8) SmemTail {
   uint64_t full[kMaxStages];
@@ -184,7 +188,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       for (int i = 0; i < 2; ++i) {
         ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[i]), 1);
-        ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[i]), 4 * CTAS);
+        ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[i]), kEpilogueWarps * CTAS);
       }
       tail->abort_flag = 0u;
       ptx::fence_mbar_init();
@@ -369,19 +373,22 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     // peer CTA of a pair: the leader issues the MMAs for both
   } else {
     // ---------------------------------------------------------- epilogue
-    const int q = warp & 3;  // TMEM lane quadrant this warp may read
-    const uint32_t my_out = out_base + uint32_t(q) * 2u * kStageOutBytes;
+    const int q = warp & 3;            // TMEM lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
+    const int col_base = half * (kBlockN / 2);
+    const uint32_t my_out = out_base + uint32_t(warp - 2) * kStageOutBytes;
     TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
     Tile t;
     uint32_t it = 0;
     uint32_t stores = 0;  // TMA stores this warp has issued (lane 0's bulk groups)
     bool ok = true;
 
-    // One 32-column chunk `v` of this lane's row: either into the staging buffer
-    // and out through a TMA store (whole warp valid), or straight to global.
-    auto emit = [&](const uint32_t (&v)[32], int ch, bool warp_full, bool row_ok,
+    // One 32-column chunk `v` (fp32 bits) of this lane's row, starting at column
+    // `col` of the tile: through the staging buffer and a TMA store when the
+    // whole warp's rows exist, else straight to global for the rows that do.
+    auto emit = [&](const uint32_t (&v)[32], int col, bool warp_full, bool row_ok,
                     __nv_bfloat16* crow, int cols_left, int tile_row, int col0) {
-      if (ch * 32 >= cols_left) return;  // chunk lies entirely past the last column
+      if (col >= cols_left) return;  // chunk lies entirely past the last column
       uint4 o[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
@@ -396,12 +403,11 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         o[j].w = *reinterpret_cast<uint32_t*>(&h);
       }
       if (warp_full) {
-        const uint32_t buf = my_out + (stores & 1u) * kStageOutBytes;
-        // The store issued two chunks ago read this buffer; it must be done reading.
-        if (lane == 0 && stores >= 2) ptx::bulk_wait_group_read<1>();
+        // The previous store read this buffer; it must be done reading.
+        if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<0>();
         __syncwarp();
         // 64-byte swizzle: 16-byte chunk index ^= (row / 2) % 4.
-        const uint32_t row_addr = buf + uint32_t(lane) * 64u;
+        const uint32_t row_addr = my_out + uint32_t(lane) * 64u;
         const uint32_t sw = (uint32_t(lane) >> 1) & 3u;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -413,15 +419,15 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_2d(&map_c, buf, col0 + ch * 32, tile_row);
+          ptx::tma_store_2d(&map_c, my_out, col0 + col, tile_row);
           ptx::bulk_commit_group();
         }
         ++stores;
       } else if (row_ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const int col = ch * 32 + j * 8;
-          if (col < cols_left) *reinterpret_cast<uint4*>(crow + col) = o[j];
+          const int cj = col + j * 8;
+          if (cj < cols_left) *reinterpret_cast<uint4*>(crow + cj) = o[j];
         }
       }
     };
@@ -435,28 +441,29 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       __nv_bfloat16* crow = c + (out_row0 + r) * p.n + t.col0;
       const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp
       const int cols_left = static_cast<int>(p.n) - t.col0;  // multiple of 8
+      uint32_t va[32], vb[32];
       if (nkb == 0) {
-        if (row_ok) {
-          const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-          for (int col = 0; col < kBlockN && col < cols_left; col += 8)
-            *reinterpret_cast<uint4*>(crow + col) = zero;
-        }
+        // Empty wgrad expert: its block of the output is zeros, same store path.
+#pragma unroll
+        for (int i = 0; i < 32; ++i) va[i] = 0u;
+#pragma unroll 1
+        for (int ch = 0; ch < kBlockN / 64; ++ch)
+          emit(va, col_base + ch * 32, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
         continue;
       }
       const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
       ++it;
       if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[ab]), aph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
-      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN;
-      uint32_t va[32], vb[32];
+      const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN + col_base;
       ptx::tmem_ld_32x32(taddr, va);
 #pragma unroll 1
-      for (int ch = 0; ch < kBlockN / 32; ch += 2) {
+      for (int ch = 0; ch < kBlockN / 64; ch += 2) {
         ptx::tmem_ld_wait();
         ptx::tmem_ld_32x32(taddr + (ch + 1) * 32, vb);
-        emit(va, ch, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
+        emit(va, col_base + ch * 32, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
         ptx::tmem_ld_wait();
-        if (ch + 2 < kBlockN / 32) {
+        if (ch + 2 < kBlockN / 64) {
           ptx::tmem_ld_32x32(taddr + (ch + 2) * 32, va);
         } else {
           // Every column has been read: hand the accumulator back before the last stores.
@@ -468,7 +475,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             else ptx::mbar_arrive(te_bar);
           }
         }
-        emit(vb, ch + 1, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
+        emit(vb, col_base + (ch + 1) * 32, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
       }
     }
     // Shared memory must outlive the stores that still read it.

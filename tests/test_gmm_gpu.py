@@ -274,6 +274,76 @@ def test_full_size_wgrad_properties(gg):
     assert torch.equal(gg.backend.gmm(a, grad, bs, trans_a=True), w)
 
 
+def test_down_projection_config3_full_size(gg):
+    """BASELINE config 3's second projection, b [8, 14336, 4096]: forward, dgrad
+    and wgrad at full size, sampled against the oracle, plus the exact doubling
+    property."""
+    import bench
+    sizes = bench.mixtral_batch_sizes()
+    starts = np.concatenate([[0], np.cumsum(sizes)])
+    g = torch.Generator(device="cuda").manual_seed(3)
+    a = torch.randn(32768, 14336, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(8, 14336, 4096, device="cuda", generator=g) * 0.02).bfloat16()
+    grad = torch.randn(32768, 4096, device="cuda", generator=g).bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    out = gg.backend.gmm(a, b, bs)
+    dx = gg.backend.gmm(grad, b, bs, trans_b=True)
+    dw = gg.backend.gmm(a, grad, bs, trans_a=True)
+    assert out.shape == (32768, 4096) and dx.shape == (32768, 14336) and dw.shape == (8, 14336, 4096)
+    for e in (1, 2, 4):
+        rows = torch.tensor([int(starts[e]), int(starts[e + 1]) - 1], device="cuda")
+        one = torch.tensor([2])
+        util.assert_close(out[rows], gmm_oracle.gmm(a[rows].cpu(), b[e:e + 1].cpu(), one), what=f"fwd expert {e}")
+        util.assert_close(dx[rows], gmm_oracle.gmm(grad[rows].cpu(), b[e:e + 1].cpu(), one, trans_b=True),
+                          what=f"dgrad expert {e}")
+        sl = slice(int(starts[e]), int(starts[e + 1]))
+        want = (a[sl, 7000:7064].float().t() @ grad[sl, 1000:1064].float()).cpu()
+        util.assert_close(dw[e, 7000:7064, 1000:1064], want.bfloat16(), rtol=1e-2, atol=1.0, what=f"wgrad expert {e}")
+    assert torch.equal(gg.backend.gmm(a * 2, b, bs), out * 2)
+    assert torch.equal(gg.backend.gmm(a, grad * 2, bs, trans_a=True), dw * 2)
+
+
+def test_fine_grained_moe_config4_full_size(gg):
+    """BASELINE config 4 at full size (z=256, k=7168, n=2048, 65536 rows, 51 empty
+    experts, offsets beyond 2^31): sampled rows of small, large and 1-row
+    experts against the oracle; empty experts' wgrad blocks are exactly zero;
+    doubling is exact; a second run is bit-identical."""
+    import bench
+    sizes = bench.fine_grained_batch_sizes()
+    starts = np.concatenate([[0], np.cumsum(sizes)])
+    g = torch.Generator(device="cuda").manual_seed(2)
+    a = torch.randn(65536, 7168, device="cuda", generator=g).bfloat16()
+    b = (torch.randn(256, 7168, 2048, device="cuda", generator=g) * 0.02).bfloat16()
+    grad = torch.randn(65536, 2048, device="cuda", generator=g).bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    out = gg.backend.gmm(a, b, bs)
+    order = np.argsort(sizes)
+    nonempty = [int(e) for e in order if sizes[e] > 0]
+    picks = nonempty[:3] + nonempty[len(nonempty) // 2:len(nonempty) // 2 + 2] + nonempty[-2:] + [255 if sizes[255] else nonempty[-3]]
+    one = torch.tensor([2])
+    for e in picks:
+        rows = torch.tensor([int(starts[e]), int(starts[e + 1]) - 1], device="cuda")
+        util.assert_close(out[rows], gmm_oracle.gmm(a[rows].cpu(), b[e:e + 1].cpu(), one), what=f"fwd expert {e}")
+    assert torch.equal(gg.backend.gmm(a * 2, b, bs), out * 2)
+    dx = gg.backend.gmm(grad, b, bs, trans_b=True)
+    for e in picks[:4]:
+        rows = torch.tensor([int(starts[e]), int(starts[e + 1]) - 1], device="cuda")
+        util.assert_close(dx[rows], gmm_oracle.gmm(grad[rows].cpu(), b[e:e + 1].cpu(), one, trans_b=True),
+                          what=f"dgrad expert {e}")
+    del out, dx
+    dw = torch.full((256, 7168, 2048), 3.0, dtype=torch.bfloat16, device="cuda")
+    gg.backend.gmm(a, grad, bs, trans_a=True, c=dw)
+    for e in range(256):
+        if sizes[e] == 0:
+            assert bool((dw[e] == 0).all()), f"empty expert {e} not zeroed"
+    for e in picks[:5]:
+        sl = slice(int(starts[e]), int(starts[e + 1]))
+        want = (a[sl, 3000:3064].float().t() @ grad[sl, 500:564].float()).cpu()
+        util.assert_close(dw[e, 3000:3064, 500:564], want.bfloat16(), rtol=1e-2, atol=0.5, what=f"wgrad expert {e}")
+    again = gg.backend.gmm(a, grad, bs, trans_a=True)
+    assert torch.equal(again, dw)
+
+
 def test_fine_grained_moe_config4_reduced_width(gg):
     """BASELINE config 4's routing (256 experts, Zipf popularity, ~20 % empty,
     65536 rows) at reduced hidden sizes so the CPU oracle stays in seconds."""
