@@ -615,14 +615,20 @@ def measure_multi(args):
 
 
 def run_profile_case(args):
-    """--profile PASS: allocate only that pass's operands at the Mixtral size
-    and launch it a few times; meant to be wrapped in ncu (one kernel, one
-    captured launch).  Prints the CUDA-event time of the last launch."""
+    """--profile PASS: allocate only that pass's operands (Mixtral size, or
+    BASELINE config 4 with --profile-workload fine) and launch it a few times;
+    meant to be wrapped in ncu (one kernel, one captured launch).  Prints the
+    CUDA-event time of the last launch."""
     from grouped_gemm_b200 import backend
     dev = torch.device("cuda", 0)
-    z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["k"], MIXTRAL["n"]
+    if args.profile_workload == "fine":
+        z, rows, k, n = 256, 65536, 7168, 2048
+        sizes = fine_grained_batch_sizes()
+    else:
+        z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["k"], MIXTRAL["n"]
+        sizes = mixtral_batch_sizes()
     g = torch.Generator(device=dev).manual_seed(1)
-    bs = torch.tensor(mixtral_batch_sizes(), dtype=torch.int64, device=dev)
+    bs = torch.tensor(sizes, dtype=torch.int64, device=dev)
     if args.profile == "fwd":
         a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
         b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
@@ -650,6 +656,7 @@ def main():
     ap.add_argument("--profile", choices=["fwd", "dgrad", "wgrad"], default=None,
                     help="launch one pass of the Mixtral workload a few times and exit (for ncu)")
     ap.add_argument("--profile-launches", type=int, default=2)
+    ap.add_argument("--profile-workload", choices=["mixtral", "fine"], default="mixtral")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

@@ -25,12 +25,16 @@ def gg():
     return grouped_gemm_b200
 
 
-@pytest.fixture(autouse=True, params=["1", "2"], ids=["one-cta", "cta-pair"])
+@pytest.fixture(autouse=True, params=["1", "2", "auto"], ids=["one-cta", "cta-pair", "auto"])
 def _variant(request, monkeypatch, gg):
     """Every test runs on both kernel variants: tiles owned by one CTA, and tiles
-    owned by a pair of CTAs (tcgen05 cta_group::2).  The library reads the
-    variable on each call."""
-    monkeypatch.setenv("B200GMM_CTAS", request.param)
+    owned by a pair of CTAs (tcgen05 cta_group::2), and once with the library's
+    own choice of variant.  The
+    library reads the variable on each call."""
+    if request.param == "auto":
+        monkeypatch.delenv("B200GMM_CTAS", raising=False)
+    else:
+        monkeypatch.setenv("B200GMM_CTAS", request.param)
     yield request.param
     assert gg.backend.device_status() == 0, "a kernel raised a status bit (timeout / bad sizes)"
 
