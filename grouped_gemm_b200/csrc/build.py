@@ -1,4 +1,4 @@
-"""Build libb200gmm.so in-tree with nvcc for sm_100a.
+"""Build libb200gmm.so (nvcc, sm_100a) and the torch extension module in-tree.
 
 Usage: ``python grouped_gemm_b200/csrc/build.py [--force] [--verbose]`` (run it
 as a script: importing the package first would try to load the library).
@@ -57,5 +57,43 @@ def build(force=False, verbose=False):
     return LIB
 
 
+EXT_NAME = "b200gmm_torch_binding"
+EXT_DIR = os.path.join(HERE, "torch_ext")
+EXT_SRC = os.path.join(EXT_DIR, "binding.cpp")
+EXT_BUILD = os.path.join(EXT_DIR, "build")
+EXT_LIB = os.path.join(EXT_BUILD, EXT_NAME + ".so")
+
+
+def binding_is_stale():
+    if not os.path.exists(EXT_LIB):
+        return True
+    built = os.path.getmtime(EXT_LIB)
+    return any(os.path.getmtime(d) > built for d in (EXT_SRC, os.path.join(ROOT, "include", "b200gmm.h")))
+
+
+def build_torch_binding(force=False, verbose=False):
+    """Compile the torch extension module (torch_ext/binding.cpp) in-tree.  It is
+    plain C++ (no device code): argument checks, stream and workspace from torch,
+    then the C ABI of libb200gmm.so, which it finds through its rpath."""
+    if not force and not binding_is_stale():
+        return EXT_LIB
+    build(force=False, verbose=verbose)  # the extension links against the library
+    from torch.utils.cpp_extension import load
+    os.makedirs(EXT_BUILD, exist_ok=True)
+    load(name=EXT_NAME, sources=[EXT_SRC], extra_include_paths=[os.path.join(ROOT, "include")],
+         extra_cflags=["-O2", "-std=c++17"],
+         extra_ldflags=["-L" + HERE, "-lb200gmm", "-Wl,-rpath,$ORIGIN/../..", "-Wl,-rpath," + HERE],
+         build_directory=EXT_BUILD, with_cuda=True, verbose=verbose, is_python_module=False)
+    if not os.path.exists(EXT_LIB):
+        raise RuntimeError("torch extension build did not produce " + EXT_LIB)
+    os.utime(EXT_LIB, None)
+    return EXT_LIB
+
+
+def build_all(force=False, verbose=False):
+    return build(force=force, verbose=verbose), build_torch_binding(force=force, verbose=verbose)
+
+
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    for path in build_all(force="--force" in sys.argv, verbose="--verbose" in sys.argv):
+        print(path)

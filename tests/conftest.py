@@ -21,7 +21,7 @@ def _build_libraries():
     spec = importlib.util.spec_from_file_location("b200gmm_build", path)
     build_lib = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(build_lib)
-    build_lib.build()
+    build_lib.build_all()
     from oracle import build as build_oracle
     build_oracle.build()
 

@@ -362,6 +362,62 @@ def test_fine_grained_moe_config4_reduced_width(gg):
     _check_fwd_bwd(gg, a_cpu, b_cpu, bs_cpu, False, True, ref_stat=False)
 
 
+def test_degenerate_shapes(gg):
+    """Nothing to multiply: no rows, no experts' worth of work, k == 0."""
+    dev = "cuda"
+    bf = torch.bfloat16
+    # no rows at all: forward returns an empty result, wgrad zeros
+    a0 = torch.zeros(0, 64, device=dev, dtype=bf)
+    b = torch.randn(3, 64, 128, device=dev).to(bf)
+    bs0 = torch.zeros(3, dtype=torch.int64, device=dev)
+    assert gg.backend.gmm(a0, b, bs0).shape == (0, 128)
+    c = torch.full((3, 64, 128), 5.0, device=dev, dtype=bf)
+    gg.backend.gmm(a0, torch.zeros(0, 128, device=dev, dtype=bf), bs0, trans_a=True, c=c)
+    assert bool((c == 0).all())
+    # rows exist but every expert is empty: c untouched, wgrad zeros
+    a = torch.randn(10, 64, device=dev).to(bf)
+    c = torch.full((10, 128), 5.0, device=dev, dtype=bf)
+    gg.backend.gmm(a, b, bs0, c=c)
+    assert bool((c == 5.0).all())
+    c3 = torch.full((3, 64, 128), 5.0, device=dev, dtype=bf)
+    gg.backend.gmm(a, torch.randn(10, 128, device=dev).to(bf), bs0, trans_a=True, c=c3)
+    assert bool((c3 == 0).all())
+    # k == 0: an empty sum per element
+    c = torch.full((10, 128), 5.0, device=dev, dtype=bf)
+    gg.backend.gmm(torch.zeros(10, 0, device=dev, dtype=bf), torch.zeros(3, 0, 128, device=dev, dtype=bf),
+                   torch.tensor([4, 6, 0], device=dev), c=c)
+    assert bool((c == 0).all())
+
+
+def test_rejected_arguments_launch_nothing(gg):
+    from grouped_gemm_b200 import _capi
+    a = torch.randn(16, 60, device="cuda").bfloat16()          # 60 is not a multiple of 8
+    b = torch.randn(1, 60, 64, device="cuda").bfloat16()
+    before = _capi.launch_count()
+    with pytest.raises(RuntimeError, match="multiples of 8"):
+        gg.backend.gmm(a, b, torch.tensor([16], device="cuda"))
+    with pytest.raises(RuntimeError, match="too many experts"):
+        gg.backend.gmm(torch.zeros(8, 64, device="cuda", dtype=torch.bfloat16),
+                       torch.zeros(1025, 64, 64, device="cuda", dtype=torch.bfloat16),
+                       torch.zeros(1025, dtype=torch.int64, device="cuda"))
+    assert _capi.launch_count() == before
+
+
+def test_non_default_stream_and_second_device_guard(gg):
+    """Work goes to the caller's current stream."""
+    torch.manual_seed(9)
+    a = torch.randn(300, 128, device="cuda").bfloat16()
+    b = (torch.randn(2, 128, 256, device="cuda") * 0.1).bfloat16()
+    bs = torch.tensor([100, 200], device="cuda")
+    want = gg.backend.gmm(a, b, bs)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        got = gg.backend.gmm(a, b, bs)
+    side.synchronize()
+    assert torch.equal(got, want)
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
