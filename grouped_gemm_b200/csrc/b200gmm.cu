@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -34,6 +35,33 @@ EncodeTiledFn encode_tiled_fn() {
     return reinterpret_cast<EncodeTiledFn>(p);
   }();
   return fn;
+}
+
+typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+
+CtxGetCurrentFn ctx_get_current_fn() {
+  static CtxGetCurrentFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    return reinterpret_cast<CtxGetCurrentFn>(p);
+  }();
+  return fn;
+}
+
+// cuTensorMapEncodeTiled is a driver call and fails with "invalid context" on a
+// thread that has a CUDA device selected but no context bound yet (e.g. an
+// autograd worker whose allocations all came from a cache).  Binding the
+// device's primary context to the calling thread is what cudaSetDevice does.
+int ensure_context(int dev) {
+  CtxGetCurrentFn get = ctx_get_current_fn();
+  CUcontext ctx = nullptr;
+  if (get != nullptr && get(&ctx) == CUDA_SUCCESS && ctx != nullptr) return B200GMM_OK;
+  if (cudaSetDevice(dev) != cudaSuccess) return B200GMM_ECUDA;
+  if (get != nullptr && (get(&ctx) != CUDA_SUCCESS || ctx == nullptr)) return B200GMM_ECUDA;
+  return B200GMM_OK;
 }
 
 struct DeviceInfo {
@@ -74,6 +102,7 @@ int device_info(DeviceInfo** out) {
   static DeviceInfo infos[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200GMM_ECUDA;
+  if (ensure_context(dev) != B200GMM_OK) return B200GMM_ECUDA;
   std::lock_guard<std::mutex> lock(mu);
   DeviceInfo& d = infos[dev];
   if (d.sm_count == 0) {
@@ -119,6 +148,11 @@ int device_info(DeviceInfo** out) {
   return B200GMM_OK;
 }
 
+int env_int(const char* name, int fallback) {
+  const char* v = std::getenv(name);
+  return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
+}
+
 // bf16 tensor map (128-byte swizzle unless told otherwise); dims/box innermost first.
 int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
@@ -139,12 +173,12 @@ int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
                         const_cast<void*>(base), gdim, gstride, gbox, estride,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && env_int("B200GMM_DEBUG", 0) != 0) {
+    std::fprintf(stderr, "b200gmm: cuTensorMapEncodeTiled -> %d: base %p rank %d dims {%llu,%llu,%llu} box {%u,%u,%u}\n",
+                 static_cast<int>(r), base, rank, (unsigned long long)gdim[0], (unsigned long long)gdim[1],
+                 (unsigned long long)(rank > 2 ? gdim[2] : 0), gbox[0], gbox[1], rank > 2 ? gbox[2] : 0u);
+  }
   return r == CUDA_SUCCESS ? B200GMM_OK : B200GMM_ETENSORMAP;
-}
-
-int env_int(const char* name, int fallback) {
-  const char* v = std::getenv(name);
-  return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
 }
 
 // Which variant a problem runs on.  Only shapes known on the host may decide

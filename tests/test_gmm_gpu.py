@@ -418,6 +418,33 @@ def test_non_default_stream_and_second_device_guard(gg):
     assert torch.equal(got, want)
 
 
+def test_call_from_thread_without_bound_context(gg):
+    """A thread that has never made a CUDA call of its own (an autograd worker
+    served entirely from the allocator cache looks like this) can run gmm: the
+    library binds the device's context before it builds tensor maps."""
+    import threading
+    a = torch.randn(368, 512, device="cuda").bfloat16()
+    b = (torch.randn(4, 256, 512, device="cuda") * 0.05).bfloat16()
+    bs = torch.tensor([200, 0, 37, 131], device="cuda")
+    want = gg.backend.gmm(a, b, bs, trans_b=True)
+    c = torch.empty_like(want)
+    torch.cuda.synchronize()
+    errors = []
+
+    def work():
+        try:
+            gg.backend.gmm(a, b, bs, trans_b=True, c=c)
+        except Exception as e:  # noqa: BLE001
+            errors.append(e)
+
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    torch.cuda.synchronize()
+    assert not errors, errors
+    assert torch.equal(c, want)
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
