@@ -19,8 +19,13 @@ namespace b200gmm {
 
 constexpr int kPushThreads = 256;
 
+constexpr int kPushVecsPerThread = 8;  // 16-byte loads a thread keeps in flight
+
 // item i: row src_row[i] (or i when src_row == nullptr) of `src`
 //      -> row dst_row[i] of the buffer peer_base[dst_rank[i]].
+// One CTA moves one row at a time: every thread first issues all of its loads of
+// the row (up to kPushVecsPerThread x 16 bytes, i.e. rows of up to 32 KiB in one
+// sweep), then all of its stores, so that a whole row is in flight per CTA.
 __global__ void __launch_bounds__(kPushThreads)
 push_rows_kernel(const uint4* __restrict__ src, int64_t row_vecs, int64_t n_items,
                  const int32_t* __restrict__ src_row, const int32_t* __restrict__ dst_rank,
@@ -29,19 +34,19 @@ push_rows_kernel(const uint4* __restrict__ src, int64_t row_vecs, int64_t n_item
     const int64_t sr = (src_row != nullptr) ? src_row[item] : item;
     const uint4* s = src + sr * row_vecs;
     uint4* d = static_cast<uint4*>(peer_base[dst_rank[item]]) + dst_row[item] * row_vecs;
-    int64_t v = threadIdx.x;
-    // four independent 16-byte loads in flight per thread before the stores
-    for (; v + 3 * kPushThreads < row_vecs; v += 4 * kPushThreads) {
-      const uint4 r0 = __ldg(s + v);
-      const uint4 r1 = __ldg(s + v + kPushThreads);
-      const uint4 r2 = __ldg(s + v + 2 * kPushThreads);
-      const uint4 r3 = __ldg(s + v + 3 * kPushThreads);
-      d[v] = r0;
-      d[v + kPushThreads] = r1;
-      d[v + 2 * kPushThreads] = r2;
-      d[v + 3 * kPushThreads] = r3;
+    for (int64_t base = 0; base < row_vecs; base += int64_t(kPushVecsPerThread) * kPushThreads) {
+      uint4 r[kPushVecsPerThread];
+#pragma unroll
+      for (int j = 0; j < kPushVecsPerThread; ++j) {
+        const int64_t v = base + int64_t(j) * kPushThreads + threadIdx.x;
+        if (v < row_vecs) r[j] = __ldg(s + v);
+      }
+#pragma unroll
+      for (int j = 0; j < kPushVecsPerThread; ++j) {
+        const int64_t v = base + int64_t(j) * kPushThreads + threadIdx.x;
+        if (v < row_vecs) d[v] = r[j];
+      }
     }
-    for (; v < row_vecs; v += kPushThreads) d[v] = __ldg(s + v);
   }
 }
 
