@@ -42,14 +42,14 @@ UNIT = "TFLOP/s"
 
 # ----------------------------------------------------------------------------- workloads
 def mixtral_batch_sizes():
-    """BASELINE config 2: multinomial(32768, Dirichlet(alpha=1)), seed 1."""
+    """benchmark configuration 2: multinomial(32768, Dirichlet(alpha=1)), seed 1."""
     rng = np.random.default_rng(1)
     p = rng.dirichlet(np.ones(8))
     return [int(v) for v in rng.multinomial(32768, p)]
 
 
 def fine_grained_batch_sizes():
-    """BASELINE config 4: 256 experts, Zipf(1.1) popularity, 51 forced empty, 65536 rows, seed 2."""
+    """benchmark configuration 4: 256 experts, Zipf(1.1) popularity, 51 forced empty, 65536 rows, seed 2."""
     rng = np.random.default_rng(2)
     perm = rng.permutation(256)
     w = np.zeros(256)
@@ -61,7 +61,7 @@ def fine_grained_batch_sizes():
 
 
 def ep_routing(tokens=65536, experts=64, top_k=4):
-    """BASELINE config 5: uniform-random top-k distinct experts per token, seed 3."""
+    """benchmark configuration 5: uniform-random top-k distinct experts per token, seed 3."""
     rng = np.random.default_rng(3)
     idx = np.argsort(rng.random((tokens, experts)), axis=1)[:, :top_k]
     return torch.from_numpy(np.ascontiguousarray(idx)).to(torch.int64)
@@ -262,12 +262,12 @@ def run_reference(args):
 # ----------------------------------------------------------------------------- our arm
 def workload_config(n_gpus):
     if n_gpus == 1:
-        return {"workload": "mixtral-8x7b expert up-projection fwd+dgrad+wgrad (BASELINE configs[2] on "
+        return {"workload": "mixtral-8x7b expert up-projection fwd+dgrad+wgrad (configs[2] of the baseline spec, on "
                             "configs[1] shapes): z=8 rows=32768 k=4096 n=14336, batch_sizes "
                             "multinomial(Dirichlet(1), seed 1), on device",
                 "batch_sizes": mixtral_batch_sizes(),
                 "l2": "inputs larger than L2 (2.1 GB read per pass, no flush)"}
-    return {"workload": f"expert-parallel projection fwd+dgrad+wgrad (BASELINE configs[4]): z=64 sharded over "
+    return {"workload": f"expert-parallel projection fwd+dgrad+wgrad (configs[4] of the baseline spec): z=64 sharded over "
                         f"{n_gpus} ranks, 65536 tokens x top-4 = 262144 rows, hidden 6144, ffn 10752, uniform "
                         "routing seed 3, dispatch/combine over NVLink",
             "parallelism": f"ep{n_gpus}",
@@ -340,10 +340,10 @@ def run_single(args):
         "algorithmic_bytes": 2.0 * (rows * k + z * k * n + rows * n),
     }
 
-    # BASELINE config 3 also names the down-projection, b [8, 14336, 4096]
+    # benchmark configuration 3 also names the down-projection, b [8, 14336, 4096]
     down = down_projection(backend, dev, bs, iters)
 
-    # small-M, HBM-bound group shapes (BASELINE config 4): report GB/s
+    # small-M, HBM-bound group shapes (benchmark configuration 4): report GB/s
     del a, b, grad
     torch.cuda.empty_cache()
     hbm = fine_grained_hbm(backend, dev, peaks)
@@ -401,7 +401,7 @@ def down_projection(backend, dev, bs, iters):
 
 
 def fine_grained_hbm(backend, dev, peaks):
-    """BASELINE config 4 (z=256, k=7168, n=2048, 65536 rows, ~20 % empty experts;
+    """benchmark configuration 4 (z=256, k=7168, n=2048, 65536 rows, ~20 % empty experts;
     median group 59 rows): the weights (forward, dgrad) or the per-expert outputs
     (wgrad) dominate the traffic, so these passes are judged against the HBM
     roofline.  Algorithmic bytes: operands + weights of non-empty experts +
@@ -647,7 +647,7 @@ def measure_multi(args):
 
 def run_profile_case(args):
     """--profile PASS: allocate only that pass's operands (Mixtral size, or
-    BASELINE config 4 with --profile-workload fine) and launch it a few times;
+    benchmark configuration 4 with --profile-workload fine) and launch it a few times;
     meant to be wrapped in ncu (one kernel, one captured launch).  Prints the
     CUDA-event time of the last launch."""
     from grouped_gemm_b200 import backend

@@ -130,7 +130,7 @@ def combine(y, plan, group=None, weights=None, reduce=True):
 
 def expert_parallel_step(x, w, grad_rows, plan, gmm_fn, group=None):
     """One forward + backward of an expert-parallel projection, the unit that
-    BASELINE config 5 times: dispatch, local forward, combine; dispatch of the
+    benchmark configuration 5 times: dispatch, local forward, combine; dispatch of the
     output gradient, local dgrad and wgrad, combine of dgrad.
 
     ``w``: this rank's experts [experts_per_rank, h_in, h_out]; ``grad_rows``:

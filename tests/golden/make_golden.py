@@ -8,9 +8,9 @@ function definitions with ``ast`` and executes them unchanged on CPU
 (``Tensor.cuda`` is made a no-op for the duration).  Nothing from the reference is
 written into this repository except the numbers its functions produce.
 
-Run in the build container, where the checkout exists:
-    python tests/golden/make_golden.py [/path/to/reference]
-The GPU box never runs this; tests read the committed .npz.
+Run where a checkout of the reference exists:
+    python tests/golden/make_golden.py /path/to/reference
+(or set GROUPED_GEMM_REFERENCE).  Tests never run this; they read the committed .npz.
 
 Cases follow the reference's grid (ops_test.py:29-36, :59-109, :143-158):
 fixed and variable batch sizes, both trans_b settings, forward and the
@@ -63,7 +63,7 @@ def variable_sizes(z, m):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref_root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("GROUPED_GEMM_REFERENCE", "reference")
     randn, ref_gmm = load_reference_functions(ref_root)
     real_cuda = torch.Tensor.cuda
     torch.Tensor.cuda = lambda self, *a, **k: self

@@ -129,7 +129,7 @@ def test_against_reference_golden(gg, key):
         util.assert_close(got, gold, rtol=1e-2, atol=1e-6, what=name)
 
 
-# ---- BASELINE config 1 -----------------------------------------------------------
+# ---- benchmark configuration 1 -----------------------------------------------------------
 @pytest.mark.parametrize("trans_b", [False, True])
 @pytest.mark.parametrize("on_device", [False, True])
 def test_config1_cpu_correctness_case(gg, trans_b, on_device):
@@ -226,7 +226,7 @@ def test_fill_offsets_bit_exact(gg, case, trans_a, trans_b):
     assert np.array_equal(out.cpu().numpy(), want)
 
 
-# ---- full BASELINE sizes: size-independent properties ------------------------------------
+# ---- full benchmark sizes: size-independent properties ------------------------------------
 def _mixtral(gg, trans_b=False):
     import bench
     torch.manual_seed(1)
@@ -279,7 +279,7 @@ def test_full_size_wgrad_properties(gg):
 
 
 def test_down_projection_config3_full_size(gg):
-    """BASELINE config 3's second projection, b [8, 14336, 4096]: forward, dgrad
+    """benchmark configuration 3's second projection, b [8, 14336, 4096]: forward, dgrad
     and wgrad at full size, sampled against the oracle, plus the exact doubling
     property."""
     import bench
@@ -308,7 +308,7 @@ def test_down_projection_config3_full_size(gg):
 
 
 def test_fine_grained_moe_config4_full_size(gg):
-    """BASELINE config 4 at full size (z=256, k=7168, n=2048, 65536 rows, 51 empty
+    """benchmark configuration 4 at full size (z=256, k=7168, n=2048, 65536 rows, 51 empty
     experts, offsets beyond 2^31): sampled rows of small, large and 1-row
     experts against the oracle; empty experts' wgrad blocks are exactly zero;
     doubling is exact; a second run is bit-identical."""
@@ -349,7 +349,7 @@ def test_fine_grained_moe_config4_full_size(gg):
 
 
 def test_fine_grained_moe_config4_reduced_width(gg):
-    """BASELINE config 4's routing (256 experts, Zipf popularity, ~20 % empty,
+    """benchmark configuration 4's routing (256 experts, Zipf popularity, ~20 % empty,
     65536 rows) at reduced hidden sizes so the CPU oracle stays in seconds."""
     import bench
     sizes = bench.fine_grained_batch_sizes()

@@ -10,7 +10,7 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLDEN = os.path.join(HERE, "golden", "ops_test_golden.npz")
 
-# BASELINE tolerance for bf16 results against an fp32-accumulated reference.
+# Required tolerance for bf16 results against an fp32-accumulated reference.
 RTOL = 1e-2
 ATOL = 1e-2
 
