@@ -570,8 +570,12 @@ def measure_multi(args):
     if args.exchange == "peer":
         per = EP["tokens"] // world
         px = ep.PeerExchange(ep_routing()[rank * per:(rank + 1) * per].to(dev), EP["z"], EP["hidden"], EP["ffn"])
-        step = (lambda: px.step_overlapped(x, w, grad, gmm_fn)) if args.overlap else (
-            lambda: px.step(x, w, grad, gmm_fn))
+        if args.overlap:
+            step = lambda: px.step_overlapped(x, w, grad, gmm_fn)
+        elif args.no_fused_combine:
+            step = lambda: px.step(x, w, grad, gmm_fn)
+        else:
+            step = lambda: px.step_fused(x, w, grad, gmm_fn)
         exchange_step = step
     else:
         step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
@@ -630,7 +634,10 @@ def measure_multi(args):
                          "achieved": ep_flops() / world / ms_gemm / 1e9, "peak": peaks["sustained"],
                          "unit": "TFLOP/s", "frac": ep_flops() / world / ms_gemm / 1e9 / peaks["sustained"],
                          "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (per GPU)", "traffic": None},
-            "exchange": (("peer memory: b200gmm_push_rows over NVLink (symmetric memory), 4 pushes per step"
+            "exchange": (("peer memory over NVLink (symmetric memory): "
+                          + ("4 row pushes per step" if (args.no_fused_combine or args.overlap) else
+                             "2 row pushes (dispatch) per step, both combines written by the GEMM epilogues "
+                             "straight into the token owners' buffers")
                           + (", on a second stream under the GEMMs" if args.overlap else ""))
                          if args.exchange == "peer" else "NCCL all_to_all_single + index gathers"),
             "exchange_share": 1.0 - ms_gemm / ms_step, "ms_gemm_per_step": ms_gemm,
@@ -698,6 +705,8 @@ def main():
     ap.add_argument("--overlap", action="store_true",
                     help="multi-GPU runs: issue the exchanges on a second stream under the GEMMs "
                          "(measured: +3 %% at 8 GPUs, -5 %% at 2 GPUs, so off by default)")
+    ap.add_argument("--no-fused-combine", action="store_true",
+                    help="multi-GPU runs: combine with separate push kernels instead of from the GEMM epilogues")
     ap.add_argument("--no-scaling-base", action="store_true",
                     help="multi-GPU runs: skip timing the same workload on rank 0's GPU alone")
     ap.add_argument("--scaling-base", action="store_true",

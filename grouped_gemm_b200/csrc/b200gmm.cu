@@ -74,7 +74,7 @@ struct DeviceInfo {
 template <int MODE, int CTAS>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
                        const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
-                       CUtensorMap* slots) {
+                       CUtensorMap* slots, const int64_t* row_dest) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
@@ -87,7 +87,7 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, map_c, c, bs, p, status, slots);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, map_c, c, bs, p, status, slots, row_dest);
 }
 
 template <int MODE, int CTAS>
@@ -266,10 +266,21 @@ int b200gmm_workspace_bytes(int z, size_t* out_bytes) {
   return B200GMM_OK;
 }
 
-int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_sizes,
-                int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
-                int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
-                uint32_t* device_status, void* cuda_stream) {
+}  // extern "C"
+
+namespace {
+
+// Shared body of b200gmm_run and b200gmm_run_scatter.  row_dest == nullptr: rows
+// go to c.  Otherwise (non-transposed a only) row i of the result goes to the
+// address row_dest[i] and c is not touched.
+int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
+             int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
+             int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
+             uint32_t* device_status, void* cuda_stream, const int64_t* row_dest) {
+  if (row_dest != nullptr) {
+    if (trans_a || dim_a1 == 0) return B200GMM_EINVAL;
+    if (c == nullptr) c = const_cast<void*>(a);  // never written; keeps the argument checks below uniform
+  }
   Problem p;
   int ctas = choose_ctas(z, tokens, dim_a1, trans_a);
   int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p);
@@ -351,9 +362,10 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
   }
 
   // Output map for the epilogue's TMA stores: 32 x 32 boxes, 64-byte swizzle.
-  // wgrad's c[z, m, n] is addressed as z*m rows.
-  CUtensorMap map_c;
-  {
+  // wgrad's c[z, m, n] is addressed as z*m rows.  Unused (left zeroed) when the
+  // rows are scattered through row_dest.
+  CUtensorMap map_c = {};
+  if (row_dest == nullptr) {
     const uint64_t dc[2] = {N, p.mode == kTN ? Z * D1 : T};
     const uint32_t bc[2] = {32, 32};
     if (dc[1] >= (uint64_t(1) << 31)) return B200GMM_ELIMIT;
@@ -364,14 +376,14 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
   cudaError_t err;
   if (ctas == 2) {
     const int grid = dev->pair_ctas < kMaxCtas ? dev->pair_ctas : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
   } else {
     const int grid = dev->sm_count < kMaxCtas ? dev->sm_count : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots);
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
@@ -379,6 +391,27 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
   }
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return B200GMM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_sizes,
+                int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
+                int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
+                uint32_t* device_status, void* cuda_stream) {
+  return run_impl(a, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, trans_a, trans_b,
+                  workspace, workspace_bytes, device_status, cuda_stream, nullptr);
+}
+
+int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest, const int64_t* batch_sizes,
+                        int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
+                        int trans_b, void* workspace, size_t workspace_bytes, uint32_t* device_status,
+                        void* cuda_stream) {
+  if (row_dest == nullptr) return B200GMM_EINVAL;
+  return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
+                  workspace, workspace_bytes, device_status, cuda_stream, row_dest);
 }
 
 int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* batch_sizes,

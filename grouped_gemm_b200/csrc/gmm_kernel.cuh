@@ -157,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
            const int64_t* __restrict__ batch_sizes, const Problem p,
-           uint32_t* status, CUtensorMap* map_slots) {
+           uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest) {
   using G = Geometry<CTAS>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
@@ -386,6 +386,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     // One 32-column chunk `v` (fp32 bits) of this lane's row, starting at column
     // `col` of the tile: through the staging buffer and a TMA store when the
     // whole warp's rows exist, else straight to global for the rows that do.
+    const bool scatter_rows = (MODE != kTN) && (row_dest != nullptr);
     auto emit = [&](const uint32_t (&v)[32], int col, bool warp_full, bool row_ok,
                     __nv_bfloat16* crow, int cols_left, int tile_row, int col0) {
       if (col >= cols_left) return;  // chunk lies entirely past the last column
@@ -423,6 +424,24 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           ptx::bulk_commit_group();
         }
         ++stores;
+      } else if (scatter_rows) {
+        // Row-scatter mode: this lane's 64-byte piece goes through its own slice
+        // of the staging buffer (linear, no swizzle) and leaves as one bulk
+        // async copy, so the thread never waits on the (possibly remote) write.
+        if (row_ok) {
+          if (stores > 0) ptx::bulk_wait_group_read<0>();  // this lane's previous copy
+          const uint32_t row_addr = my_out + uint32_t(lane) * 64u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(row_addr + (uint32_t(j) << 4)),
+                         "r"(o[j].x), "r"(o[j].y), "r"(o[j].z), "r"(o[j].w)
+                         : "memory");
+          ptx::fence_proxy_async_smem();
+          const int left = cols_left - col;
+          ptx::bulk_store_1d(crow + col, row_addr, left < 32 ? uint32_t(left) * 2u : 64u);
+          ptx::bulk_commit_group();
+        }
+        ++stores;
       } else if (row_ok) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -436,9 +455,15 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
       const int r = row_off + q * 32 + lane;  // row inside the (pair) tile
       const bool row_ok = r < t.valid_rows;
-      const bool warp_full = !p.direct_store && (row_off + q * 32 + 31) < t.valid_rows;
+      // row_dest != nullptr (expert-parallel combine fused into this epilogue):
+      // output row i does not go to c[i] but to the address row_dest[i], which may
+      // be a row of a buffer on another GPU; such rows are written with plain
+      // stores by the lane that holds them.
+      const bool scatter = (MODE != kTN) && (row_dest != nullptr);
+      const bool warp_full = !p.direct_store && !scatter && (row_off + q * 32 + 31) < t.valid_rows;
       const int64_t out_row0 = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0) : int64_t(t.row0);
       __nv_bfloat16* crow = c + (out_row0 + r) * p.n + t.col0;
+      if (scatter && row_ok) crow = reinterpret_cast<__nv_bfloat16*>(row_dest[out_row0 + r]) + t.col0;
       const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp
       const int cols_left = static_cast<int>(p.n) - t.col0;  // multiple of 8
       uint32_t va[32], vb[32];
@@ -479,7 +504,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
     }
     // Shared memory must outlive the stores that still read it.
-    if (lane == 0) ptx::bulk_wait_group_all();
+    if (lane == 0 || scatter_rows) ptx::bulk_wait_group_all();
     __syncwarp();
   }
 

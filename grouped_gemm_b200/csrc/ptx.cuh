@@ -120,6 +120,15 @@ __device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src, int 
                : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1)
                : "memory");
 }
+// shared -> global copy of `bytes` contiguous bytes (multiple of 16, both
+// addresses 16-byte aligned); bulk async group of the issuing thread.  The
+// destination may be memory of another GPU mapped into this process.
+__device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+               :
+               : "l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

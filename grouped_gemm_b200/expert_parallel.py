@@ -274,6 +274,14 @@ class PeerExchange:
         self.back_rank = origin[: self.local_rows, 0].contiguous()
         self.back_row = origin[: self.local_rows, 1].to(torch.int64).contiguous()
         self.comm_stream = torch.cuda.Stream(device=device)
+        # Final address of every grouped row on the rank that owns its token, for
+        # the GEMMs that write their result straight there (step_fused).
+        out_bases = self._t_out[self.back_rank.long()]
+        da_bases = self._t_da[self.back_rank.long()]
+        self.dest_out = (out_bases + self.back_row * (h_out * esize)).contiguous()
+        self.dest_da = (da_bases + self.back_row * (h_in * esize)).contiguous()
+        self._ws_bytes = _capi.workspace_bytes(self.per_rank)
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
 
     # -- plumbing ---------------------------------------------------------------
     def barrier(self):
@@ -374,3 +382,29 @@ class PeerExchange:
         compute.wait_event(finished)
         dx.record_stream(compute)
         return self.out_slots[: self.num_tokens * self.top_k], dx, dw
+
+    def _gmm_scatter(self, a, w, dest, trans_b):
+        """Local grouped GEMM whose epilogue writes row i to address dest[i]."""
+        n = w.shape[1] if trans_b else w.shape[2]
+        ws = torch.empty(self._ws_bytes, dtype=torch.uint8, device=self.device)
+        rc = self._lib.b200gmm_run_scatter(
+            a.data_ptr(), w.data_ptr(), dest.data_ptr(), self.batch_sizes.data_ptr(), 1,
+            self.per_rank, a.shape[0], a.shape[1], n, 1 if trans_b else 0,
+            ws.data_ptr(), self._ws_bytes, self._status.data_ptr(),
+            torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "b200gmm_run_scatter")
+
+    def step_fused(self, x, w, grad_rows, gmm_fn):
+        """``step`` with both combines fused into the GEMMs: the forward and the
+        dgrad kernels write each result row from their epilogue straight into the
+        token owner's buffer (over NVLink when the owner is another GPU), so only
+        the two dispatches remain as separate passes.  Same results as ``step``."""
+        pairs = self.num_tokens * self.top_k
+        a = self.dispatch(x)
+        self._gmm_scatter(a, w, self.dest_out, False)
+        g = self.dispatch_rows(grad_rows)      # its barrier also publishes the forward's rows
+        self._gmm_scatter(g, w, self.dest_da, True)
+        dw = gmm_fn(a, g, self.batch_sizes, True, False)
+        self.barrier()                         # dgrad rows have arrived everywhere
+        dx = self.da_slots[:pairs].view(self.num_tokens, self.top_k, self.h_in).sum(1)
+        return self.out_slots[:pairs], dx, dw

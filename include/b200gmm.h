@@ -133,6 +133,26 @@ int b200gmm_run_static(const void* a, const void* b, void* c,
                        uint32_t* device_status, void* cuda_stream);
 
 /*
+ * b200gmm_run (trans_a = 0 only) with the expert-parallel combine fused into the
+ * kernel's epilogue: row i of the result is not written to a c tensor but to the
+ * address row_dest[i] (device array of `tokens` byte addresses, each 16-byte
+ * aligned, each the start of an n-element bf16 row).  The addresses may point
+ * into buffers on other GPUs that are mapped into this process (symmetric memory
+ * or CUDA IPC): rows then leave over NVLink with plain stores while the tensor
+ * cores work on the next tile, and no separate gather / all-to-all / scatter pass
+ * over the output is needed.  Remote memory is only written.  The caller orders
+ * the kernel against the readers on the other GPUs (a barrier after it).  Rows
+ * past sum(batch_sizes) are not written.  Other arguments as in b200gmm_run.
+ * The reference has no counterpart (single GPU; its callers un-sort the output
+ * themselves).
+ */
+int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
+                        const int64_t* batch_sizes, int batch_sizes_on_device,
+                        int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
+                        void* workspace, size_t workspace_bytes,
+                        uint32_t* device_status, void* cuda_stream);
+
+/*
  * Row exchange for expert parallelism: copy `n_items` rows of `row_bytes` bytes
  * (a multiple of 16) from `src` on this GPU into rows of buffers that may live
  * on other GPUs.  Item i reads row src_row[i] of `src` (row i when src_row is

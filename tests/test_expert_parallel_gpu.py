@@ -89,6 +89,9 @@ def test_peer_exchange_single_rank_matches_oracle():
     o2, dx2, dw2 = px.step_overlapped(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
     torch.cuda.synchronize()
     assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw)
+    o3, dx3, dw3 = px.step_fused(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
+    torch.cuda.synchronize()
+    assert torch.equal(o3, out_rows) and torch.equal(dx3, dx) and torch.equal(dw3, dw)
     want_rows, want_dx, want_dw = _unsharded_oracle()
     assert _close(out_rows, want_rows) and _close(dx, want_dx, 5e-2) and _close(dw, want_dw, 5e-2)
     assert bool((dw[Z - 1] == 0).all())
@@ -121,9 +124,13 @@ def _worker(rank, world, port, results):
         o2, dx2, dw2 = o2.clone(), dx2.clone(), dw2.clone()
         for _ in range(3):   # replayed steps reuse the buffers: the barriers must order them
             o3, dx3, dw3 = px.step_overlapped(xl, wl, gl, gmm_fn)
+        o3, dx3, dw3 = o3.clone(), dx3.clone(), dw3.clone()
+        for _ in range(3):   # combines fused into the GEMM epilogues (stores into the peer's buffer)
+            o4, dx4, dw4 = px.step_fused(xl, wl, gl, gmm_fn)
         torch.cuda.synchronize()
         same = bool(torch.equal(o1, o2) and torch.equal(dw1, dw2) and torch.equal(dx1, dx2)
-                    and torch.equal(o3, o2) and torch.equal(dw3, dw2) and torch.equal(dx3, dx2))
+                    and torch.equal(o3, o2) and torch.equal(dw3, dw2) and torch.equal(dx3, dx2)
+                    and torch.equal(o4, o2) and torch.equal(dw4, dw2) and torch.equal(dx4, dx2))
         results[rank] = (same, o2.cpu(), dx2.float().cpu(), dw2.cpu(), backend.device_status(dev))
     finally:
         dist.destroy_process_group()
