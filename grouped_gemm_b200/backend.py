@@ -39,6 +39,43 @@ def gmm(a, b, batch_sizes, trans_a=False, trans_b=False, c=None):
     return out
 
 
+def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False):
+    """``gmm`` with the un-sort fused into the kernel: row ``i`` of the grouped
+    result is written to ``out[row_index[i]]`` instead of ``c[i]`` (no
+    counterpart in the reference, whose callers un-permute ``c`` themselves).
+
+    ``a`` [T, k] holds the rows sorted by expert as for ``gmm``; ``out`` is a
+    contiguous bf16 [R, n] tensor on the same device, ``row_index`` int64 [T] with
+    values in [0, R).  Rows of ``out`` that no index names are left alone; if two
+    indices coincide the later write wins in no defined order.  Returns ``out``."""
+    assert a.ndim == 2 and b.ndim == 3 and batch_sizes.ndim == 1 and out.ndim == 2 and row_index.ndim == 1
+    n = b.shape[1] if trans_b else b.shape[2]
+    k = b.shape[2] if trans_b else b.shape[1]
+    if not (a.is_cuda and b.is_cuda and out.is_cuda and row_index.is_cuda):
+        raise RuntimeError("gmm_scatter: a, b, out and row_index must be CUDA tensors")
+    if not (a.dtype == b.dtype == out.dtype == torch.bfloat16) or row_index.dtype != torch.int64:
+        raise RuntimeError("gmm_scatter: a, b, out must be bfloat16 and row_index int64")
+    if a.shape[1] != k or out.shape[1] != n or row_index.shape[0] != a.shape[0] or batch_sizes.shape[0] != b.shape[0]:
+        raise RuntimeError("gmm_scatter: shapes of a, b, out, row_index and batch_sizes do not fit together")
+    if not (a.is_contiguous() and b.is_contiguous() and out.is_contiguous()):
+        raise RuntimeError("gmm_scatter: a, b and out must be contiguous")
+    if batch_sizes.dtype != torch.int64:
+        raise RuntimeError("gmm_scatter: batch_sizes must be int64")
+    lib = _capi.load()
+    z = batch_sizes.shape[0]
+    with torch.cuda.device(a.device):
+        dest = row_index * (n * 2) + out.data_ptr()          # byte address of every destination row
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        rc = lib.b200gmm_run_scatter(
+            a.data_ptr(), b.data_ptr(), dest.data_ptr(), bs.data_ptr(), 1 if bs.is_cuda else 0, z,
+            a.shape[0], a.shape[1], n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
+            backend.device_status(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
+    _capi.check(rc, "b200gmm_run_scatter")
+    return out
+
+
 def device_status(device="cuda"):
     """Status bits raised by the kernels on ``device`` since the process began
     (0 = none; see B200GMM_STATUS_* in include/b200gmm.h).  Synchronises."""

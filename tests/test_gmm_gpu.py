@@ -445,6 +445,31 @@ def test_call_from_thread_without_bound_context(gg):
     assert torch.equal(c, want)
 
 
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("on_device", [False, True])
+def test_gmm_scatter_unsorts_in_the_epilogue(gg, trans_b, on_device):
+    """gmm_scatter(a, b, bs, out, perm) == scatter of gmm(a, b, bs) by perm, bit for bit;
+    rows no index names stay untouched."""
+    torch.manual_seed(11)
+    sizes = [300, 0, 5, 700, 129, 64]
+    T, k, n = sum(sizes), 256, 328
+    a = torch.randn(T, k, device="cuda").bfloat16()
+    b = (torch.randn(len(sizes), n, k, device="cuda") if trans_b else torch.randn(len(sizes), k, n, device="cuda")).bfloat16() * 0.1
+    bs = torch.tensor(sizes, dtype=torch.int64)
+    if on_device:
+        bs = bs.cuda()
+    want_rows = gg.backend.gmm(a, b, bs, trans_b=trans_b)
+    R = T + 7
+    perm = torch.randperm(R, device="cuda")[:T]
+    out = torch.full((R, n), 9.0, device="cuda", dtype=torch.bfloat16)
+    got = gg.backend.gmm_scatter(a, b, bs, out, perm, trans_b=trans_b)
+    assert got is out
+    want = torch.full((R, n), 9.0, device="cuda", dtype=torch.bfloat16)
+    want[perm] = want_rows
+    assert torch.equal(out, want)
+    util.assert_close(want_rows, gmm_oracle.gmm(a.cpu(), b.cpu(), bs.cpu(), trans_b=trans_b), atol=2e-2, what="rows")
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
