@@ -567,9 +567,24 @@ def measure_multi(args):
     dist.barrier()
     ep, plan, x, w, grad = ep_setup(world, rank, dev)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
+    exchange_note = ""
+    px = None
     if args.exchange == "peer":
         per = EP["tokens"] // world
-        px = ep.PeerExchange(ep_routing()[rank * per:(rank + 1) * per].to(dev), EP["z"], EP["hidden"], EP["ffn"])
+        try:
+            px = ep.PeerExchange(ep_routing()[rank * per:(rank + 1) * per].to(dev), EP["z"], EP["hidden"], EP["ffn"])
+            failed = 0
+        except Exception as exc:  # noqa: BLE001  (symmetric memory unavailable on this box)
+            exchange_note = f" (peer-memory setup failed, NCCL exchange used instead: {type(exc).__name__}: {exc})"[:300]
+            failed = 1
+        # every rank takes the same path
+        agree = torch.tensor([failed], device=dev)
+        dist.all_reduce(agree, op=dist.ReduceOp.MAX)
+        if int(agree.item()):
+            px = None
+            args.exchange = "nccl"
+            exchange_note = exchange_note or " (peer-memory setup failed on another rank, NCCL exchange used instead)"
+    if px is not None:
         if args.overlap:
             step = lambda: px.step_overlapped(x, w, grad, gmm_fn)
         elif args.no_fused_combine:
@@ -639,7 +654,7 @@ def measure_multi(args):
                              "2 row pushes (dispatch) per step, both combines written by the GEMM epilogues "
                              "straight into the token owners' buffers")
                           + (", on a second stream under the GEMMs" if args.overlap else ""))
-                         if args.exchange == "peer" else "NCCL all_to_all_single + index gathers"),
+                         if args.exchange == "peer" else "NCCL all_to_all_single + index gathers" + exchange_note),
             "exchange_share": 1.0 - ms_gemm / ms_step, "ms_gemm_per_step": ms_gemm,
             "scaling_base": scaling_base,
             "cpu_baseline": None,
