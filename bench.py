@@ -173,15 +173,27 @@ def timed_region(fn, steps, world):
 
 
 # ----------------------------------------------------------------------------- CPU baseline
-def cpu_sample_inputs(frac):
-    """The Mixtral workload with each expert's rows cut to ``frac`` of its size
-    (full k and n, full weights)."""
-    sizes = [max(1, int(s * frac)) for s in mixtral_batch_sizes()]
+def cpu_workload(n_gpus):
+    """Shapes the CPU reference runs: the N=1 workload (Mixtral up-projection) or,
+    for N>1, the expert-parallel projection with a subset of its 64 experts (all
+    of them would need 8 GB of host weights for no change in the per-row rate)."""
+    if n_gpus == 1:
+        return {"name": "mixtral up-projection", "sizes": mixtral_batch_sizes(), "k": MIXTRAL["k"],
+                "n": MIXTRAL["n"], "experts_total": MIXTRAL["z"]}
+    counts = torch.bincount(ep_routing().reshape(-1), minlength=EP["z"]).tolist()
+    return {"name": "expert-parallel projection, first 8 of 64 experts", "sizes": counts[:8],
+            "k": EP["hidden"], "n": EP["ffn"], "experts_total": EP["z"]}
+
+
+def cpu_sample_inputs(work, frac):
+    """The workload with each expert's rows cut to ``frac`` of its size (full k
+    and n, full weights of the sampled experts)."""
+    sizes = [max(1, int(s * frac)) for s in work["sizes"]]
     rows = sum(sizes)
     g = torch.Generator().manual_seed(1)
-    a = torch.randn(rows, MIXTRAL["k"], generator=g).bfloat16()
-    b = (torch.randn(MIXTRAL["z"], MIXTRAL["k"], MIXTRAL["n"], generator=g) * 0.02).bfloat16()
-    grad = torch.randn(rows, MIXTRAL["n"], generator=g).bfloat16()
+    a = torch.randn(rows, work["k"], generator=g).bfloat16()
+    b = (torch.randn(len(sizes), work["k"], work["n"], generator=g) * 0.02).bfloat16()
+    grad = torch.randn(rows, work["n"], generator=g).bfloat16()
     return sizes, a, b, grad
 
 
@@ -193,17 +205,24 @@ def cpu_step(sizes, a, b, grad):
     gmm_oracle.torch_loop_bf16(a, b, bs, trans_b=False)
     gmm_oracle.torch_loop_bf16(grad, b, bs, trans_b=True)
     gmm_oracle.torch_loop_tn_bf16(a, grad, bs)
-    return 3 * 2.0 * sum(sizes) * MIXTRAL["k"] * MIXTRAL["n"]
+    return 3 * 2.0 * sum(sizes) * a.shape[1] * grad.shape[1]
 
 
-def pick_cpu_sample(target_s):
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU arm is meant to use the host."""
+    cores = os.cpu_count() or 1
+    if torch.get_num_threads() < cores:
+        torch.set_num_threads(cores)
+
+
+def pick_cpu_sample(work, target_s):
     """Inputs of the CPU sample whose step takes about ``target_s`` seconds on
     this host (at most the full workload).  Small samples run far below the
     host's large-matrix rate, so the sample is grown until one step is long
     enough.  Returns (frac, sizes, a, b, grad, seconds of the last step)."""
     frac = 1.0 / 256
     while True:
-        sizes, a, b, grad = cpu_sample_inputs(frac)
+        sizes, a, b, grad = cpu_sample_inputs(work, frac)
         cpu_step(sizes, a, b, grad)  # warm-up (thread pool, primitive caches)
         t0 = time.perf_counter()
         cpu_step(sizes, a, b, grad)
@@ -213,17 +232,23 @@ def pick_cpu_sample(target_s):
         frac = min(1.0, frac * min(8.0, target_s / dt))
 
 
+def cpu_sample_text(work, sizes, frac):
+    return (f"per-expert torch.matmul loop (bf16, CPU), {work['name']}: {sum(sizes)} of {sum(work['sizes'])} rows "
+            f"of {len(sizes)} experts (each cut to {frac:.4f} of its rows), k={work['k']} n={work['n']}, "
+            "full weights of those experts, fwd+dgrad+wgrad")
+
+
 def cpu_baseline(target_s=12.0):
-    frac, sizes, a, b, grad, _ = pick_cpu_sample(target_s)
+    use_all_host_threads()
+    work = cpu_workload(1)
+    frac, sizes, a, b, grad, _ = pick_cpu_sample(work, target_s)
     t0 = time.perf_counter()
     flops = cpu_step(sizes, a, b, grad)
     dt = time.perf_counter() - t0
     return {
         "value": flops / dt / 1e12, "unit": UNIT, "cores": torch.get_num_threads(),
         "host_cpus": os.cpu_count(), "kind": "port",
-        "sample": f"per-expert torch.matmul loop (bf16, CPU) on {sum(sizes)} of {MIXTRAL['rows']} rows "
-                  f"(each expert cut to {frac:.4f} of its rows), full k/n/weights, fwd+dgrad+wgrad, "
-                  f"one pass of {dt:.1f} s",
+        "sample": cpu_sample_text(work, sizes, frac) + f", one pass of {dt:.1f} s",
     }
 
 
@@ -234,7 +259,9 @@ def run_reference(args):
     world, rank, _ = dist_info()
     if rank != 0:
         return
-    frac, sizes, a, b, grad, _ = pick_cpu_sample(3.0)
+    use_all_host_threads()
+    work = cpu_workload(args.gpus)
+    frac, sizes, a, b, grad, _ = pick_cpu_sample(work, 3.0)
     for _ in range(args.warmup):
         cpu_step(sizes, a, b, grad)
     t0 = time.perf_counter()
@@ -243,8 +270,7 @@ def run_reference(args):
         flops += cpu_step(sizes, a, b, grad)
     dt = time.perf_counter() - t0
     value = flops / dt / 1e12
-    sample = (f"per-expert torch.matmul loop (bf16, CPU) on {sum(sizes)} of {MIXTRAL['rows']} rows per step "
-              f"(each expert cut to {frac:.4f} of its rows), full k/n/weights")
+    sample = cpu_sample_text(work, sizes, frac) + ", per step"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
