@@ -470,6 +470,44 @@ def test_gmm_scatter_unsorts_in_the_epilogue(gg, trans_b, on_device):
     util.assert_close(want_rows, gmm_oracle.gmm(a.cpu(), b.cpu(), bs.cpu(), trans_b=trans_b), atol=2e-2, what="rows")
 
 
+def test_randomised_shapes_against_oracle(gg):
+    """Seeded random group sizes (tiny, tile-boundary, large, mostly empty), odd
+    dimensions, all three layouts, batch sizes on either side: every case against
+    the CPU oracle; rows past sum(batch_sizes) must stay untouched."""
+    import random
+    rng = random.Random(2024)
+    torch.manual_seed(2024)
+    edge = [0, 1, 7, 63, 64, 65, 127, 128, 129, 255, 256, 257, 300, 511, 513]
+    for case in range(40):
+        z = rng.choice([1, 2, 3, 5, 8, 17, 40])
+        style = rng.choice(["tiny", "edge", "sparse"])
+        if style == "tiny":
+            sizes = [rng.randint(0, 40) for _ in range(z)]
+        elif style == "edge":
+            sizes = [rng.choice(edge) for _ in range(z)]
+        else:
+            sizes = [rng.choice([0, 0, 0, rng.randint(1, 400)]) for _ in range(z)]
+        T, d1, n = sum(sizes), rng.choice([8, 16, 72, 128, 200, 264]), rng.choice([8, 24, 64, 136, 256, 328])
+        mode, pad = rng.choice(["nn", "nt", "tn"]), rng.choice([0, 3])
+        bs_cpu = torch.tensor(sizes, dtype=torch.int64)
+        bs = bs_cpu.cuda() if rng.random() < 0.5 else bs_cpu
+        a = torch.randn(T + pad, d1).bfloat16()
+        what = f"case {case}: {mode} sizes={sizes[:8]} d1={d1} n={n}"
+        if mode == "tn":
+            b = torch.randn(T + pad, n).bfloat16()
+            c = torch.full((z, d1, n), 3.0, dtype=torch.bfloat16, device="cuda")
+            gg.backend.gmm(a.cuda(), b.cuda(), bs, trans_a=True, c=c)
+            want = gmm_oracle.gmm(a, b, bs_cpu, trans_a=True)
+            util.assert_close(c, want, rtol=1e-2, atol=max(1e-2, 2e-3 * float(want.abs().max())), what=what)
+        else:
+            b = ((torch.randn(z, n, d1) if mode == "nt" else torch.randn(z, d1, n)) * 0.2).bfloat16()
+            c = torch.full((T + pad, n), 3.0, dtype=torch.bfloat16, device="cuda")
+            gg.backend.gmm(a.cuda(), b.cuda(), bs, trans_b=(mode == "nt"), c=c)
+            want = gmm_oracle.gmm(a, b, bs_cpu, trans_b=(mode == "nt"))
+            util.assert_close(c[:T], want[:T], rtol=1e-2, atol=2e-2, what=what)
+            assert bool((c[T:] == 3.0).all()), what + ": rows past sum(batch_sizes) written"
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
