@@ -76,6 +76,57 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False):
     return out
 
 
+def gmm_gather(x, row_index, b, batch_sizes, trans_b=False, c=None, out=None, out_index=None):
+    """``gmm(x[row_index], b, batch_sizes, trans_b)`` without materialising
+    ``x[row_index]``: the kernel gathers the rows of ``x`` while it loads its
+    operand tiles (no counterpart in the reference, whose callers permute the
+    activations into a new tensor first).
+
+    ``x`` bf16 [R, k]; ``row_index`` integer [T] with values in [0, R), listing for
+    every grouped row (sorted by expert, as ``gmm`` expects them) the row of ``x``
+    it comes from.  Result rows go to ``c`` [T, n] (allocated if omitted), or, when
+    ``out`` [R2, n] and ``out_index`` int64 [T] are given, row i goes to
+    ``out[out_index[i]]`` (gather and un-sort both fused) and ``out`` is returned."""
+    assert x.ndim == 2 and b.ndim == 3 and batch_sizes.ndim == 1 and row_index.ndim == 1
+    n = b.shape[1] if trans_b else b.shape[2]
+    k = b.shape[2] if trans_b else b.shape[1]
+    if not (x.is_cuda and b.is_cuda and row_index.is_cuda):
+        raise RuntimeError("gmm_gather: x, b and row_index must be CUDA tensors")
+    if not (x.dtype == b.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
+        raise RuntimeError("gmm_gather: x and b must be bfloat16, batch_sizes int64")
+    if x.shape[1] != k or batch_sizes.shape[0] != b.shape[0] or not (x.is_contiguous() and b.is_contiguous()):
+        raise RuntimeError("gmm_gather: shapes of x, b and batch_sizes do not fit together, or not contiguous")
+    tokens = row_index.shape[0]
+    idx32 = row_index.to(torch.int32).contiguous()
+    lib = _capi.load()
+    z = batch_sizes.shape[0]
+    with torch.cuda.device(x.device):
+        dest_ptr = None
+        result = None
+        if out is not None:
+            if out_index is None or out.dtype != torch.bfloat16 or not out.is_contiguous() or out.shape[1] != n \
+                    or out_index.shape[0] != tokens:
+                raise RuntimeError("gmm_gather: out must be contiguous bf16 [R2, n] with out_index int64 [T]")
+            dest = out_index.to(torch.int64) * (n * 2) + out.data_ptr()
+            dest_ptr, result = dest.data_ptr(), out
+            c_ptr = None
+        else:
+            if c is None:
+                c = torch.empty(tokens, n, device=x.device, dtype=x.dtype)
+            elif c.shape != (tokens, n) or c.dtype != torch.bfloat16 or not c.is_contiguous():
+                raise RuntimeError("gmm_gather: c must be contiguous bf16 [len(row_index), n]")
+            c_ptr, result = c.data_ptr(), c
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        rc = lib.b200gmm_run_gather(
+            x.data_ptr(), x.shape[0], idx32.data_ptr(), b.data_ptr(), c_ptr, dest_ptr, bs.data_ptr(),
+            1 if bs.is_cuda else 0, z, tokens, k, n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
+            backend.device_status(x.device).data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
+    _capi.check(rc, "b200gmm_run_gather")
+    return result
+
+
 def device_status(device="cuda"):
     """Status bits raised by the kernels on ``device`` since the process began
     (0 = none; see B200GMM_STATUS_* in include/b200gmm.h).  Synchronises."""

@@ -74,7 +74,7 @@ struct DeviceInfo {
 template <int MODE, int CTAS>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
                        const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
-                       CUtensorMap* slots, const int64_t* row_dest) {
+                       CUtensorMap* slots, const int64_t* row_dest, const int32_t* a_rows) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(kThreads);
@@ -87,7 +87,7 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, map_c, c, bs, p, status, slots, row_dest);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, map_c, c, bs, p, status, slots, row_dest, a_rows);
 }
 
 template <int MODE, int CTAS>
@@ -276,7 +276,9 @@ namespace {
 int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
              int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
-             uint32_t* device_status, void* cuda_stream, const int64_t* row_dest) {
+             uint32_t* device_status, void* cuda_stream, const int64_t* row_dest,
+             const int32_t* a_rows = nullptr, int64_t a_source_rows = 0) {
+  if (a_rows != nullptr && (trans_a || dim_a1 == 0 || a_source_rows <= 0)) return B200GMM_EINVAL;
   if (row_dest != nullptr) {
     if (trans_a || dim_a1 == 0) return B200GMM_EINVAL;
     if (c == nullptr) c = const_cast<void*>(a);  // never written; keeps the argument checks below uniform
@@ -339,16 +341,18 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
 
   CUtensorMap map_a, map_b;
   const uint64_t T = uint64_t(tokens), D1 = uint64_t(dim_a1), N = uint64_t(n), Z = uint64_t(z);
+  const uint64_t a_map_rows = (a_rows != nullptr) ? uint64_t(a_source_rows) : T;
+  const uint32_t a_box_rows = (a_rows != nullptr) ? 1u : uint32_t(kBlockM);  // gather4: one-row box
   if (p.mode == kNN) {
-    const uint64_t da[2] = {D1, T};
-    const uint32_t ba[2] = {kBlockK, kBlockM};
+    const uint64_t da[2] = {D1, a_map_rows};
+    const uint32_t ba[2] = {kBlockK, a_box_rows};
     const uint64_t db[3] = {N, D1, Z};
     const uint32_t bb[3] = {64, kBlockK, 1};
     if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
       return rc;
   } else if (p.mode == kNT) {
-    const uint64_t da[2] = {D1, T};
-    const uint32_t ba[2] = {kBlockK, kBlockM};
+    const uint64_t da[2] = {D1, a_map_rows};
+    const uint32_t ba[2] = {kBlockK, a_box_rows};
     const uint64_t db[3] = {D1, N, Z};
     const uint32_t bb[3] = {kBlockK, uint32_t(kBlockN / ctas), 1};
     if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
@@ -376,14 +380,14 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   cudaError_t err;
   if (ctas == 2) {
     const int grid = dev->pair_ctas < kMaxCtas ? dev->pair_ctas : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
   } else {
     const int grid = dev->sm_count < kMaxCtas ? dev->sm_count : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
@@ -412,6 +416,16 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest, c
   if (row_dest == nullptr) return B200GMM_EINVAL;
   return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
                   workspace, workspace_bytes, device_status, cuda_stream, row_dest);
+}
+
+int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index, const void* b, void* c,
+                       const int64_t* row_dest, const int64_t* batch_sizes, int batch_sizes_on_device,
+                       int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b, void* workspace,
+                       size_t workspace_bytes, uint32_t* device_status, void* cuda_stream) {
+  if (row_index == nullptr || x_rows <= 0 || x_rows >= (int64_t(1) << 31)) return B200GMM_EINVAL;
+  if (c == nullptr && row_dest == nullptr) return B200GMM_EINVAL;
+  return run_impl(x, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
+                  workspace_bytes, device_status, cuda_stream, row_dest, row_index, x_rows);
 }
 
 int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* batch_sizes,

@@ -157,7 +157,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
            const int64_t* __restrict__ batch_sizes, const Problem p,
-           uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest) {
+           uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest,
+           const int32_t* __restrict__ a_rows) {
   using G = Geometry<CTAS>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
@@ -235,7 +236,64 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       __syncwarp();
     }
-    if (lane == 0) {
+    if (MODE != kTN && a_rows != nullptr) {
+      // Gathered A (the caller's sort-by-expert fused into the load): row i of
+      // the grouped operand is row a_rows[i] of the tensor behind map_a, whose
+      // box is one row high.  The whole warp produces: lane l fetches rows
+      // 4l .. 4l+3 of this CTA's 128-row tile with one gather4 per k-block, lane 0
+      // also does the waiting, the expect_tx and the B loads.
+      TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+      Tile t;
+      uint32_t s = 0, ph = 0;
+      bool ok = true;
+      while (ok && walk.next(&t)) {
+        const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+        int idx[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int r = row_off + 4 * lane + j;  // row inside the (pair) tile
+          // rows that do not exist are never stored: any readable row will do
+          idx[j] = (r < t.valid_rows) ? a_rows[t.row0 + r] : 0;
+        }
+        for (int kb = 0; kb < nkb; ++kb) {
+          const uint32_t local_bar = ptx::smem_u32(&tail->full[s]);
+          const uint32_t sa = stage_base + s * G::kStageBytes;
+          const uint32_t sb = sa + G::kABytes;
+          const int k0 = kb * kBlockK;
+          if (lane == 0) ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          const uint32_t bar = kPair ? ptx::mapa(local_bar, 0) : local_bar;
+          if (lane == 0) {
+            if (!kPair) {
+              ptx::mbar_arrive_expect_tx(local_bar, G::kStageBytes);
+              if (MODE == kNN) {
+#pragma unroll
+                for (int j = 0; j < G::kBCols / 64; ++j)
+                  ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, k0, t.expert);
+              } else {
+                ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0, t.expert);
+              }
+            } else {
+              if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * G::kStageBytes);
+              if (MODE == kNN) {
+#pragma unroll
+                for (int j = 0; j < G::kBCols / 64; ++j)
+                  ptx::tma_load_3d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, k0,
+                                        t.expert);
+              } else {
+                ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
+              }
+            }
+          }
+          // 4 rows x 128 bytes per lane, 128 rows x 128 bytes per warp: the same
+          // K-major 128-byte-swizzled tile an ordinary box load would leave.
+          if (kPair) ptx::tma_gather4_2d_pair(sa + lane * 512u, &map_a, bar, k0, idx[0], idx[1], idx[2], idx[3]);
+          else ptx::tma_gather4_2d(sa + lane * 512u, &map_a, bar, k0, idx[0], idx[1], idx[2], idx[3]);
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+      }
+    } else if (lane == 0) {
       TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
       Tile t;
       uint32_t s = 0, ph = 0;

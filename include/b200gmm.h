@@ -153,6 +153,24 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
                         uint32_t* device_status, void* cuda_stream);
 
 /*
+ * b200gmm_run (trans_a = 0 only) with the caller's sort-by-expert fused into the
+ * operand load: row i of the grouped left operand is row row_index[i] of `x`
+ * (bf16 [x_rows, dim_a1], contiguous; row_index: device int32 [tokens], values in
+ * [0, x_rows)).  The kernel fetches those rows with TMA gather loads, four rows
+ * per instruction, so no permuted copy of the activations is ever written.
+ * Results go to c[i] as in b200gmm_run, or, if row_dest is non-NULL, to the
+ * addresses row_dest[i] as in b200gmm_run_scatter (c may then be NULL).
+ * The reference has no counterpart: its callers gather the rows into a new
+ * tensor before calling gmm.
+ */
+int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index,
+                       const void* b, void* c, const int64_t* row_dest,
+                       const int64_t* batch_sizes, int batch_sizes_on_device,
+                       int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
+                       void* workspace, size_t workspace_bytes,
+                       uint32_t* device_status, void* cuda_stream);
+
+/*
  * Row exchange for expert parallelism: copy `n_items` rows of `row_bytes` bytes
  * (a multiple of 16) from `src` on this GPU into rows of buffers that may live
  * on other GPUs.  Item i reads row src_row[i] of `src` (row i when src_row is

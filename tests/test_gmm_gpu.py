@@ -508,6 +508,30 @@ def test_randomised_shapes_against_oracle(gg):
             assert bool((c[T:] == 3.0).all()), what + ": rows past sum(batch_sizes) written"
 
 
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_gmm_gather_fuses_the_sort_by_expert(gg, trans_b):
+    """gmm_gather(x, idx, ...) == gmm(x[idx], ...) bit for bit (same tiles, same
+    arithmetic; only the way the rows reach shared memory differs), also with the
+    un-sort fused on the way out."""
+    torch.manual_seed(13)
+    sizes = [300, 0, 5, 700, 129, 64, 1, 513]
+    T, k, n, R = sum(sizes), 200, 328, 900
+    x = torch.randn(R, k, device="cuda").bfloat16()
+    idx = torch.randint(0, R, (T,), device="cuda")            # tokens may repeat (top-k routing)
+    b = (torch.randn(len(sizes), n, k, device="cuda") if trans_b else torch.randn(len(sizes), k, n, device="cuda")).bfloat16() * 0.1
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    want = gg.backend.gmm(x[idx].contiguous(), b, bs, trans_b=trans_b)
+    got = gg.backend.gmm_gather(x, idx, b, bs, trans_b=trans_b)
+    assert torch.equal(got, want)
+    util.assert_close(want, gmm_oracle.gmm(x[idx].cpu(), b.cpu(), bs.cpu(), trans_b=trans_b), atol=2e-2, what="rows")
+    perm = torch.randperm(T + 4, device="cuda")[:T]
+    out = torch.full((T + 4, n), 9.0, device="cuda", dtype=torch.bfloat16)
+    gg.backend.gmm_gather(x, idx, b, bs, trans_b=trans_b, out=out, out_index=perm)
+    ref = torch.full((T + 4, n), 9.0, device="cuda", dtype=torch.bfloat16)
+    ref[perm] = want
+    assert torch.equal(out, ref)
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
