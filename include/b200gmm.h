@@ -158,6 +158,11 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
  * (bf16 [x_rows, dim_a1], contiguous; row_index: device int32 [tokens], values in
  * [0, x_rows)).  The kernel fetches those rows with TMA gather loads, four rows
  * per instruction, so no permuted copy of the activations is ever written.
+ * Cost: a gather load moves 512 bytes and the TMA unit retires roughly one per
+ * 60 cycles, far below what the tensor pipe consumes; on the Mixtral forward
+ * shape this entry point takes 9.3 ms against 2.8 - 3.3 ms for a separate gather
+ * followed by b200gmm_run.  It is for callers that cannot afford the permuted
+ * copy in memory, not a faster path.
  * Results go to c[i] as in b200gmm_run, or, if row_dest is non-NULL, to the
  * addresses row_dest[i] as in b200gmm_run_scatter (c may then be NULL).
  * The reference has no counterpart: its callers gather the rows into a new
