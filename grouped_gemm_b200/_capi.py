@@ -21,6 +21,7 @@ STATIC_MAX_EXPERTS = 256
 STATUS_TIMEOUT = 0x1
 STATUS_NEGATIVE_SIZE = 0x2
 STATUS_ROWS_OVERFLOW = 0x4
+STATUS_BAD_ROW_INDEX = 0x8
 
 # name -> (restype, argtypes); exactly the symbols include/b200gmm.h declares.
 _c = ctypes

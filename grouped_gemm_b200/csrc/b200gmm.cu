@@ -71,13 +71,14 @@ struct DeviceInfo {
   bool attrs_set = false;
 };
 
-template <int MODE, int CTAS>
+template <int MODE, int CTAS, bool GATHER = false>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
                        const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
-                       CUtensorMap* slots, const int64_t* row_dest, const int32_t* a_rows) {
+                       CUtensorMap* slots, const int64_t* row_dest, const int32_t* a_rows = nullptr,
+                       const __nv_bfloat16* a_src = nullptr, int64_t a_src_rows = 0) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(GATHER ? gather_threads<CTAS>() : kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -87,12 +88,13 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS>, map_a, map_b, map_c, c, bs, p, status, slots, row_dest, a_rows);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER>, map_a, map_b, map_c, c, bs, p, status, slots,
+                            row_dest, a_rows, a_src, a_src_rows);
 }
 
-template <int MODE, int CTAS>
+template <int MODE, int CTAS, bool GATHER = false>
 cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(kSmemBytes));
 }
 
@@ -114,7 +116,9 @@ int device_info(DeviceInfo** out) {
   if (!d.attrs_set) {
     if (set_smem_attr<kNN, 1>() != cudaSuccess || set_smem_attr<kNT, 1>() != cudaSuccess ||
         set_smem_attr<kTN, 1>() != cudaSuccess || set_smem_attr<kNN, 2>() != cudaSuccess ||
-        set_smem_attr<kNT, 2>() != cudaSuccess || set_smem_attr<kTN, 2>() != cudaSuccess)
+        set_smem_attr<kNT, 2>() != cudaSuccess || set_smem_attr<kTN, 2>() != cudaSuccess ||
+        set_smem_attr<kNN, 1, true>() != cudaSuccess || set_smem_attr<kNT, 1, true>() != cudaSuccess ||
+        set_smem_attr<kNN, 2, true>() != cudaSuccess || set_smem_attr<kNT, 2, true>() != cudaSuccess)
       return B200GMM_ECUDA;
     // How many 2-CTA clusters of this kernel the device can hold at once (a GPC
     // with an odd number of free SMs leaves one out).
@@ -341,22 +345,23 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
 
   CUtensorMap map_a, map_b;
   const uint64_t T = uint64_t(tokens), D1 = uint64_t(dim_a1), N = uint64_t(n), Z = uint64_t(z);
-  const uint64_t a_map_rows = (a_rows != nullptr) ? uint64_t(a_source_rows) : T;
-  const uint32_t a_box_rows = (a_rows != nullptr) ? 1u : uint32_t(kBlockM);  // gather4: one-row box
+  const bool gather = (a_rows != nullptr);  // a is then fetched row by row, without a tensor map
   if (p.mode == kNN) {
-    const uint64_t da[2] = {D1, a_map_rows};
-    const uint32_t ba[2] = {kBlockK, a_box_rows};
+    const uint64_t da[2] = {D1, T};
+    const uint32_t ba[2] = {kBlockK, uint32_t(kBlockM)};
     const uint64_t db[3] = {N, D1, Z};
     const uint32_t bb[3] = {64, kBlockK, 1};
-    if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
-      return rc;
+    if ((rc = encode_map(&map_b, b, 3, db, bb)) != 0) return rc;
+    if (gather) map_a = map_b;
+    else if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0) return rc;
   } else if (p.mode == kNT) {
-    const uint64_t da[2] = {D1, a_map_rows};
-    const uint32_t ba[2] = {kBlockK, a_box_rows};
+    const uint64_t da[2] = {D1, T};
+    const uint32_t ba[2] = {kBlockK, uint32_t(kBlockM)};
     const uint64_t db[3] = {D1, N, Z};
     const uint32_t bb[3] = {kBlockK, uint32_t(kBlockN / ctas), 1};
-    if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0 || (rc = encode_map(&map_b, b, 3, db, bb)) != 0)
-      return rc;
+    if ((rc = encode_map(&map_b, b, 3, db, bb)) != 0) return rc;
+    if (gather) map_a = map_b;
+    else if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0) return rc;
   } else {
     const uint64_t da[2] = {D1, T};
     const uint64_t db[2] = {N, T};
@@ -378,16 +383,25 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
 
   __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(c);
   cudaError_t err;
-  if (ctas == 2) {
-    const int grid = dev->pair_ctas < kMaxCtas ? dev->pair_ctas : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
+  const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a);
+  const int max_grid = (ctas == 2) ? dev->pair_ctas : dev->sm_count;
+  const int grid = max_grid < kMaxCtas ? max_grid : kMaxCtas;
+  if (gather) {
+    if (ctas == 2) {
+      if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+    } else {
+      if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+    }
+  } else if (ctas == 2) {
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
   } else {
-    const int grid = dev->sm_count < kMaxCtas ? dev->sm_count : kMaxCtas;
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows);
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();

@@ -65,6 +65,11 @@ struct Geometry {
   static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB either way
 };
 
+// The gather variant adds one warp per ring stage; each fetches the rows of A for
+// the k-blocks that land in its stage (512 threads for a CTA pair, 448 for one CTA).
+template <int CTAS>
+constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS>::kStages; }
+
 // Epilogue staging: per epilogue warp one buffer of 32 rows x 32 bf16 columns
 // (64-byte rows, 64-byte swizzle), the source of its TMA stores.  A warp converts
 // its next chunk in registers while the previous store still reads the buffer.
@@ -152,13 +157,15 @@ struct TileWalker {
   }
 };
 
-template <int MODE, int CTAS>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int MODE, int CTAS, bool GATHER = false>
+__global__ void __launch_bounds__(GATHER ? gather_threads<CTAS>() : kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
            const int64_t* __restrict__ batch_sizes, const Problem p,
            uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest,
-           const int32_t* __restrict__ a_rows) {
+           const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
+           const int64_t a_src_rows) {
+  static_assert(!GATHER || MODE != kTN, "the gathered operand is the row-major a of a forward or dgrad product");
   using G = Geometry<CTAS>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
@@ -184,7 +191,9 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       ptx::prefetch_tensormap(&map_b);
       ptx::prefetch_tensormap(&map_c);
       for (int s = 0; s < kStages; ++s) {
-        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+        // the producer's expect_tx arrival, plus one arrival by the gather warp that owns
+        // this stage in each CTA
+        ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1 + (GATHER ? CTAS : 0));
         ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
       }
       for (int i = 0; i < 2; ++i) {
@@ -236,69 +245,14 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       __syncwarp();
     }
-    if (MODE != kTN && a_rows != nullptr) {
-      // Gathered A (the caller's sort-by-expert fused into the load): row i of
-      // the grouped operand is row a_rows[i] of the tensor behind map_a, whose
-      // box is one row high.  The whole warp produces: lane l fetches rows
-      // 4l .. 4l+3 of this CTA's 128-row tile with one gather4 per k-block, lane 0
-      // also does the waiting, the expect_tx and the B loads.
-      TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
-      Tile t;
-      uint32_t s = 0, ph = 0;
-      bool ok = true;
-      while (ok && walk.next(&t)) {
-        const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
-        int idx[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int r = row_off + 4 * lane + j;  // row inside the (pair) tile
-          // rows that do not exist are never stored: any readable row will do
-          idx[j] = (r < t.valid_rows) ? a_rows[t.row0 + r] : 0;
-        }
-        for (int kb = 0; kb < nkb; ++kb) {
-          const uint32_t local_bar = ptx::smem_u32(&tail->full[s]);
-          const uint32_t sa = stage_base + s * G::kStageBytes;
-          const uint32_t sb = sa + G::kABytes;
-          const int k0 = kb * kBlockK;
-          if (lane == 0) ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag);
-          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-          if (!ok) break;
-          const uint32_t bar = kPair ? ptx::mapa(local_bar, 0) : local_bar;
-          if (lane == 0) {
-            if (!kPair) {
-              ptx::mbar_arrive_expect_tx(local_bar, G::kStageBytes);
-              if (MODE == kNN) {
-#pragma unroll
-                for (int j = 0; j < G::kBCols / 64; ++j)
-                  ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, k0, t.expert);
-              } else {
-                ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0, t.expert);
-              }
-            } else {
-              if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * G::kStageBytes);
-              if (MODE == kNN) {
-#pragma unroll
-                for (int j = 0; j < G::kBCols / 64; ++j)
-                  ptx::tma_load_3d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, k0,
-                                        t.expert);
-              } else {
-                ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
-              }
-            }
-          }
-          // 4 rows x 128 bytes per lane, 128 rows x 128 bytes per warp: the same
-          // K-major 128-byte-swizzled tile an ordinary box load would leave.
-          if (kPair) ptx::tma_gather4_2d_pair(sa + lane * 512u, &map_a, bar, k0, idx[0], idx[1], idx[2], idx[3]);
-          else ptx::tma_gather4_2d(sa + lane * 512u, &map_a, bar, k0, idx[0], idx[1], idx[2], idx[3]);
-          if (++s == kStages) { s = 0; ph ^= 1u; }
-        }
-      }
-    } else if (lane == 0) {
+    if (lane == 0) {
       TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
       Tile t;
       uint32_t s = 0, ph = 0;
       bool ok = true;
       int slot = 0, slot_expert = -1;
+      // Bytes this CTA's TMA loads bring per stage: the gather warps fetch A themselves.
+      constexpr uint32_t kTmaBytes = GATHER ? G::kBBytes : G::kStageBytes;
       const CUtensorMap* tn_a = my_maps;
       const CUtensorMap* tn_b = my_maps + 1;
       while (ok && walk.next(&t)) {
@@ -327,14 +281,14 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           const uint32_t sb = sa + G::kABytes;
           const int k0 = kb * kBlockK;
           if (!kPair) {
-            ptx::mbar_arrive_expect_tx(local_bar, G::kStageBytes);
+            ptx::mbar_arrive_expect_tx(local_bar, kTmaBytes);
             if (MODE == kNN) {
-              ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
+              if (!GATHER) ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
                 ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, k0, t.expert);
             } else if (MODE == kNT) {
-              ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
+              if (!GATHER) ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
               ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0, t.expert);
             } else {
               const int r0 = t.k_row0 + k0;
@@ -349,16 +303,16 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             // Pair: this CTA stages rows [row0+row_off, +128) of A and columns
             // [col0+col_off, +128) of B.
             // Both CTAs' loads complete on the leader's barrier (shared::cluster address).
-            if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * G::kStageBytes);
+            if (leader) ptx::mbar_arrive_expect_tx(local_bar, 2 * kTmaBytes);
             const uint32_t bar = ptx::mapa(local_bar, 0);
             if (MODE == kNN) {
-              ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
+              if (!GATHER) ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
                 ptx::tma_load_3d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, k0,
                                       t.expert);
             } else if (MODE == kNT) {
-              ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
+              if (!GATHER) ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
               ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
             } else {
               const int r0 = t.k_row0 + k0;
@@ -429,6 +383,77 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
   } else if (warp == 1) {
     // peer CTA of a pair: the leader issues the MMAs for both
+  } else if (GATHER && warp >= 2 + kEpilogueWarps) {
+    // ---------------------------------------------------------- A-row gather
+    // The caller's sort-by-expert fused into the load: row i of the grouped
+    // operand is row a_rows[i] of a_src (rows of p.d1 elements).  Gather warp w
+    // owns ring stage w: it fills it for every k-block that lands there (every
+    // kStages-th of the stream of k-blocks, which runs on across tiles), waits for
+    // its own copies and reports the stage full, so that as with the TMA loads
+    // every stage can be in flight at once.  A warp copies this CTA's 128 x 64
+    // tile with 16-byte cp.async: eight neighbouring lanes cover the 128 bytes of
+    // one row, a lane serves rows sub, sub + 4, .. sub + 124, and writes the
+    // K-major 128-byte-swizzled layout a TMA box load would leave (16-byte chunk
+    // index ^= row % 8).
+    const int w = warp - (2 + kEpilogueWarps);  // the stage this warp owns
+    const int chunk = lane & 7;
+    const int sub = lane >> 3;
+    const uint32_t stage_addr = stage_base + uint32_t(w) * G::kStageBytes;
+    const uint32_t full_bar = kPair ? ptx::mapa(ptx::smem_u32(&tail->full[w]), 0) : ptx::smem_u32(&tail->full[w]);
+    const uint32_t empty_bar = ptx::smem_u32(&tail->empty[w]);
+    TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+    Tile t;
+    uint32_t ph = 0;  // parity of this stage's current use
+    int next = w;     // position in the stream of k-blocks of this warp's next one
+    int base = 0;     // k-blocks of the stream before the current tile
+    bool ok = true;
+    bool bad_index = false;
+    while (ok && walk.next(&t)) {
+      const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+      if (next < base + nkb) {
+        int idx[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int r = row_off + j * 4 + sub;  // row inside the (pair) tile
+          // rows that do not exist are filled with zeros and never stored; so is a
+          // row whose index lies outside a_src, which is also reported
+          idx[j] = -1;
+          if (r < t.valid_rows) {
+            const int ix = a_rows[t.row0 + r];
+            if (ix >= 0 && ix < a_src_rows) idx[j] = ix;
+            else bad_index = true;
+          }
+        }
+        for (; next < base + nkb; next += kStages) {
+          if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+          const int kcol = (next - base) * kBlockK + chunk * 8;
+          const bool in_k = kcol < p.d1;  // d1 is a multiple of 8: a chunk is all in or all out
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int r = j * 4 + sub;
+            const uint32_t dst = stage_addr + uint32_t(r) * 128u + (uint32_t(chunk ^ (r & 7)) << 4);
+            const bool live = in_k && idx[j] >= 0;
+            ptx::cp_async_16(dst, live ? static_cast<const void*>(a_src + int64_t(idx[j]) * p.d1 + kcol) : a_src,
+                             live ? 16u : 0u);
+          }
+          ptx::cp_async_wait_all();
+          // this lane's copies are complete: make them visible to the tensor core's
+          // proxy, then one arrival for the warp on the (leader's) full barrier
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (kPair) ptx::mbar_arrive_cluster(full_bar);
+            else ptx::mbar_arrive(full_bar);
+          }
+          ph ^= 1u;
+        }
+      }
+      base += nkb;
+    }
+    ptx::cp_async_wait_all();
+    if (bad_index && status != nullptr) atomicOr(status, 0x8u);
   } else {
     // ---------------------------------------------------------- epilogue
     const int q = warp & 3;            // TMEM lane quadrant this warp may read

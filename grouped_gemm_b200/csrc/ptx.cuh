@@ -112,30 +112,17 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* map, uint3
       : "memory");
 }
 
-// Four rows of a 2-D tensor, chosen by four row coordinates, into four
-// consecutive shared-memory rows (tile::gather4; the tensor map's box is one row
-// high).  `bar` is a shared::cluster mbarrier address; with a CTA pair it may be
-// the leader's barrier.
-__device__ __forceinline__ void tma_gather4_2d(uint32_t dst, const void* map, uint32_t bar, int c0,
-                                               int r0, int r1, int r2, int r3) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(r0), "r"(r1), "r"(r2),
-        "r"(r3)
-      : "memory");
+// ---------------------------------------------------------------- cp.async
+// 16 bytes global -> shared by the calling thread (not TMA: the thread gives both
+// addresses).  src_bytes == 0 writes zeros and reads nothing.  The data becomes
+// visible to the async proxy (tcgen05.mma operands) only after a
+// fence_proxy_async_smem() that follows the copy's completion.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+               : "memory");
 }
-__device__ __forceinline__ void tma_gather4_2d_pair(uint32_t dst, const void* map, uint32_t cluster_bar,
-                                                    int c0, int r0, int r1, int r2, int r3) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
-      :
-      : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(cluster_bar), "r"(c0), "r"(r0), "r"(r1),
-        "r"(r2), "r"(r3)
-      : "memory");
-}
+// Returns once every cp.async of the calling thread is complete.
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // ---------------------------------------------------------------- TMA stores
 // shared -> global tile store (bulk async group of the issuing thread).

@@ -40,6 +40,7 @@ extern "C" {
 #define B200GMM_STATUS_TIMEOUT 0x1u        /* a bounded mbarrier wait ran out */
 #define B200GMM_STATUS_NEGATIVE_SIZE 0x2u  /* a batch size was < 0 (treated as 0) */
 #define B200GMM_STATUS_ROWS_OVERFLOW 0x4u  /* sum(batch_sizes) > rows of a (clamped) */
+#define B200GMM_STATUS_BAD_ROW_INDEX 0x8u  /* run_gather: a row index outside x (read as zeros) */
 
 /* Largest number of experts b200gmm_run_static accepts (its built-in scratch is
  * sized for this many). */
@@ -156,13 +157,13 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
  * b200gmm_run (trans_a = 0 only) with the caller's sort-by-expert fused into the
  * operand load: row i of the grouped left operand is row row_index[i] of `x`
  * (bf16 [x_rows, dim_a1], contiguous; row_index: device int32 [tokens], values in
- * [0, x_rows)).  The kernel fetches those rows with TMA gather loads, four rows
- * per instruction, so no permuted copy of the activations is ever written.
- * Cost: a gather load moves 512 bytes and the TMA unit retires roughly one per
- * 60 cycles, far below what the tensor pipe consumes; on the Mixtral forward
- * shape this entry point takes 9.3 ms against 2.8 - 3.3 ms for a separate gather
- * followed by b200gmm_run.  It is for callers that cannot afford the permuted
- * copy in memory, not a faster path.
+ * [0, x_rows)).  Extra warps of the kernel fetch those rows with 16-byte
+ * cp.async copies into the swizzled tile layout the tensor core reads, so no
+ * permuted copy of the activations is ever written.  An index outside
+ * [0, x_rows) is not dereferenced: the row counts as zeros and
+ * B200GMM_STATUS_BAD_ROW_INDEX is raised.  Cost on the Mixtral forward shape:
+ * about 10 % more time than b200gmm_run on already permuted rows, on a par with
+ * a separate gather followed by b200gmm_run.
  * Results go to c[i] as in b200gmm_run, or, if row_dest is non-NULL, to the
  * addresses row_dest[i] as in b200gmm_run_scatter (c may then be NULL).
  * The reference has no counterpart: its callers gather the rows into a new

@@ -532,6 +532,47 @@ def test_gmm_gather_fuses_the_sort_by_expert(gg, trans_b):
     assert torch.equal(out, ref)
 
 
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_gmm_gather_deep_k(gg, trans_b):
+    """Many k-blocks per tile (the row copies run several k-blocks ahead of the
+    tensor core), a ragged last k-block, more tiles than CTAs."""
+    torch.manual_seed(14)
+    sizes = [1500, 0, 3000, 37, 4100, 900, 2, 1025]
+    T, k, n, R = sum(sizes), 1000, 1536, 5000
+    x = torch.randn(R, k, device="cuda").bfloat16()
+    idx = torch.randint(0, R, (T,), device="cuda")
+    b = (torch.randn(len(sizes), n, k, device="cuda") if trans_b else torch.randn(len(sizes), k, n, device="cuda")).bfloat16() * 0.05
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    want = gg.backend.gmm(x[idx].contiguous(), b, bs, trans_b=trans_b)
+    for _ in range(2):
+        got = gg.backend.gmm_gather(x, idx, b, bs, trans_b=trans_b)
+        assert torch.equal(got, want)
+    assert gg.backend.device_status() == 0
+
+
+def test_gmm_gather_row_index_out_of_range_reads_zeros(gg):
+    """A row index outside x is never dereferenced: the row counts as zeros and
+    the status word says so."""
+    torch.manual_seed(15)
+    sizes = [70, 130]
+    T, k, n, R = sum(sizes), 128, 256, 50
+    x = torch.randn(R, k, device="cuda").bfloat16()
+    idx = torch.randint(0, R, (T,), device="cuda")
+    bad = torch.tensor([3, 77, 199], device="cuda")
+    idx_bad = idx.clone()
+    idx_bad[bad] = torch.tensor([R, -1, 2**31 - 1], device="cuda")
+    b = torch.randn(2, k, n, device="cuda").bfloat16() * 0.1
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    word = gg.backend.backend.device_status("cuda")
+    want = gg.backend.gmm_gather(x, idx, b, bs)
+    assert gg.backend.device_status() == 0
+    got = gg.backend.gmm_gather(x, idx_bad, b, bs)
+    assert gg.backend.device_status() & 0x8
+    word.zero_()
+    want[bad] = 0
+    assert torch.equal(got, want)
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
