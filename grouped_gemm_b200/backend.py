@@ -130,6 +130,46 @@ def gmm_gather(x, row_index, b, batch_sizes, trans_b=False, c=None, out=None, ou
     return result
 
 
+def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False, c=None):
+    """``silu(gmm(a, b_gate)) * gmm(a, b_up)`` in one kernel: the gated first
+    half of a SwiGLU expert layer (no counterpart in the reference, whose
+    callers run ``gmm`` twice and apply the activation in a kernel of their own).
+    Both products share one fp32 accumulator tile, the gate is applied to the
+    fp32 values and the result is rounded to bf16 once, so neither product is
+    ever written to memory.  Forward only: no autograd.
+
+    ``a`` bf16 [T, k] sorted by expert as for ``gmm``; ``b_gate`` and ``b_up``
+    bf16 [z, k, n] (or [z, n, k] with ``trans_b``); returns ``c`` bf16 [T, n]."""
+    assert a.ndim == 2 and b_gate.ndim == 3 and b_up.ndim == 3 and batch_sizes.ndim == 1
+    n = b_gate.shape[1] if trans_b else b_gate.shape[2]
+    k = b_gate.shape[2] if trans_b else b_gate.shape[1]
+    if not (a.is_cuda and b_gate.is_cuda and b_up.is_cuda):
+        raise RuntimeError("gmm_swiglu: a, b_gate and b_up must be CUDA tensors")
+    if not (a.dtype == b_gate.dtype == b_up.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
+        raise RuntimeError("gmm_swiglu: a, b_gate, b_up must be bfloat16, batch_sizes int64")
+    if b_gate.shape != b_up.shape or a.shape[1] != k or batch_sizes.shape[0] != b_gate.shape[0]:
+        raise RuntimeError("gmm_swiglu: shapes of a, b_gate, b_up and batch_sizes do not fit together")
+    if not (a.is_contiguous() and b_gate.is_contiguous() and b_up.is_contiguous()):
+        raise RuntimeError("gmm_swiglu: a, b_gate and b_up must be contiguous")
+    tokens = a.shape[0]
+    if c is None:
+        c = torch.empty(tokens, n, device=a.device, dtype=a.dtype)
+    elif c.shape != (tokens, n) or c.dtype != torch.bfloat16 or not c.is_contiguous() or c.device != a.device:
+        raise RuntimeError("gmm_swiglu: c must be contiguous bf16 [T, n] on a's device")
+    lib = _capi.load()
+    z = batch_sizes.shape[0]
+    with torch.cuda.device(a.device):
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        rc = lib.b200gmm_run_swiglu(
+            a.data_ptr(), b_gate.data_ptr(), b_up.data_ptr(), c.data_ptr(), None, bs.data_ptr(),
+            1 if bs.is_cuda else 0, z, tokens, k, n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
+            backend.device_status(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
+    _capi.check(rc, "b200gmm_run_swiglu")
+    return c
+
+
 def device_status(device="cuda"):
     """Status bits raised by the kernels on ``device`` since the process began
     (0 = none; see B200GMM_STATUS_* in include/b200gmm.h).  Synchronises."""

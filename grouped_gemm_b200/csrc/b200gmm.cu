@@ -71,9 +71,9 @@ struct DeviceInfo {
   bool attrs_set = false;
 };
 
-template <int MODE, int CTAS, bool GATHER = false>
+template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                       const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
+                       const CUtensorMap& map_b2, const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
                        CUtensorMap* slots, const int64_t* row_dest, const int32_t* a_rows = nullptr,
                        const __nv_bfloat16* a_src = nullptr, int64_t a_src_rows = 0) {
   cudaLaunchConfig_t cfg = {};
@@ -88,13 +88,13 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER>, map_a, map_b, map_c, c, bs, p, status, slots,
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, map_a, map_b, map_b2, map_c, c, bs, p, status, slots,
                             row_dest, a_rows, a_src, a_src_rows);
 }
 
-template <int MODE, int CTAS, bool GATHER = false>
+template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
 cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(kSmemBytes));
 }
 
@@ -118,7 +118,9 @@ int device_info(DeviceInfo** out) {
         set_smem_attr<kTN, 1>() != cudaSuccess || set_smem_attr<kNN, 2>() != cudaSuccess ||
         set_smem_attr<kNT, 2>() != cudaSuccess || set_smem_attr<kTN, 2>() != cudaSuccess ||
         set_smem_attr<kNN, 1, true>() != cudaSuccess || set_smem_attr<kNT, 1, true>() != cudaSuccess ||
-        set_smem_attr<kNN, 2, true>() != cudaSuccess || set_smem_attr<kNT, 2, true>() != cudaSuccess)
+        set_smem_attr<kNN, 2, true>() != cudaSuccess || set_smem_attr<kNT, 2, true>() != cudaSuccess ||
+        set_smem_attr<kNN, 1, false, true>() != cudaSuccess || set_smem_attr<kNT, 1, false, true>() != cudaSuccess ||
+        set_smem_attr<kNN, 2, false, true>() != cudaSuccess || set_smem_attr<kNT, 2, false, true>() != cudaSuccess)
       return B200GMM_ECUDA;
     // How many 2-CTA clusters of this kernel the device can hold at once (a GPC
     // with an odd number of free SMs leaves one out).
@@ -281,8 +283,15 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
              int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
              uint32_t* device_status, void* cuda_stream, const int64_t* row_dest,
-             const int32_t* a_rows = nullptr, int64_t a_source_rows = 0) {
+             const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr) {
   if (a_rows != nullptr && (trans_a || dim_a1 == 0 || a_source_rows <= 0)) return B200GMM_EINVAL;
+  // b2 != nullptr: gated product silu(a @ b) * (a @ b2); n counts the columns of
+  // each of b, b2 and c, the schedule runs over 2n virtual columns.
+  const bool swiglu = (b2 != nullptr);
+  if (swiglu && (trans_a || a_rows != nullptr || (reinterpret_cast<uintptr_t>(b2) & 15))) return B200GMM_EINVAL;
+  if (swiglu && (n % 8) != 0) return B200GMM_EALIGN;
+  const int64_t n_out = n;
+  if (swiglu) n = 2 * n;
   if (row_dest != nullptr) {
     if (trans_a || dim_a1 == 0) return B200GMM_EINVAL;
     if (c == nullptr) c = const_cast<void*>(a);  // never written; keeps the argument checks below uniform
@@ -310,7 +319,7 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     if (c == nullptr) return B200GMM_EINVAL;
     if (dim_a1 == 0) {
       // k == 0: every product is an empty sum.
-      if (cudaMemsetAsync(c, 0, size_t(tokens) * size_t(n) * 2, stream) != cudaSuccess)
+      if (cudaMemsetAsync(c, 0, size_t(tokens) * size_t(n_out) * 2, stream) != cudaSuccess)
         return B200GMM_ECUDA;
       return B200GMM_OK;
     }
@@ -343,8 +352,9 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     bs_dev = static_cast<const int64_t*>(workspace);
   }
 
-  CUtensorMap map_a, map_b;
-  const uint64_t T = uint64_t(tokens), D1 = uint64_t(dim_a1), N = uint64_t(n), Z = uint64_t(z);
+  CUtensorMap map_a, map_b, map_b2;
+  // N: columns of b (and of b2, and of c); the Problem's n is twice that for the gated product.
+  const uint64_t T = uint64_t(tokens), D1 = uint64_t(dim_a1), N = uint64_t(n_out), Z = uint64_t(z);
   const bool gather = (a_rows != nullptr);  // a is then fetched row by row, without a tensor map
   if (p.mode == kNN) {
     const uint64_t da[2] = {D1, T};
@@ -352,14 +362,17 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     const uint64_t db[3] = {N, D1, Z};
     const uint32_t bb[3] = {64, kBlockK, 1};
     if ((rc = encode_map(&map_b, b, 3, db, bb)) != 0) return rc;
+    if (swiglu && (rc = encode_map(&map_b2, b2, 3, db, bb)) != 0) return rc;
     if (gather) map_a = map_b;
     else if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0) return rc;
   } else if (p.mode == kNT) {
     const uint64_t da[2] = {D1, T};
     const uint32_t ba[2] = {kBlockK, uint32_t(kBlockM)};
     const uint64_t db[3] = {D1, N, Z};
-    const uint32_t bb[3] = {kBlockK, uint32_t(kBlockN / ctas), 1};
+    // rows of b per box: a CTA's share of the tile; for the gated product half a tile from each of b, b2
+    const uint32_t bb[3] = {kBlockK, uint32_t(swiglu ? kBlockN / 2 : kBlockN / ctas), 1};
     if ((rc = encode_map(&map_b, b, 3, db, bb)) != 0) return rc;
+    if (swiglu && (rc = encode_map(&map_b2, b2, 3, db, bb)) != 0) return rc;
     if (gather) map_a = map_b;
     else if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0) return rc;
   } else {
@@ -369,6 +382,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     if ((rc = encode_map(&map_a, a, 2, da, bx)) != 0 || (rc = encode_map(&map_b, b, 2, db, bx)) != 0)
       return rc;
   }
+
+  if (!swiglu) map_b2 = map_b;  // unused by the kernel, but a valid map
 
   // Output map for the epilogue's TMA stores: 32 x 32 boxes, 64-byte swizzle.
   // wgrad's c[z, m, n] is addressed as z*m rows.  Unused (left zeroed) when the
@@ -388,20 +403,28 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   const int grid = max_grid < kMaxCtas ? max_grid : kMaxCtas;
   if (gather) {
     if (ctas == 2) {
-      if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
-      else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
     } else {
-      if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
-      else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+    }
+  } else if (swiglu) {
+    if (ctas == 2) {
+      if (p.mode == kNN) err = launch_gmm<kNN, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+      else err = launch_gmm<kNT, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    } else {
+      if (p.mode == kNN) err = launch_gmm<kNN, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+      else err = launch_gmm<kNT, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
     }
   } else if (ctas == 2) {
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
   } else {
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
@@ -440,6 +463,19 @@ int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index, 
   if (c == nullptr && row_dest == nullptr) return B200GMM_EINVAL;
   return run_impl(x, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
                   workspace_bytes, device_status, cuda_stream, row_dest, row_index, x_rows);
+}
+
+int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void* c, const int64_t* row_dest,
+                       const int64_t* batch_sizes, int batch_sizes_on_device, int z, int64_t tokens,
+                       int64_t dim_a1, int64_t n, int trans_b, void* workspace, size_t workspace_bytes,
+                       uint32_t* device_status, void* cuda_stream) {
+  if (c == nullptr && row_dest == nullptr) return B200GMM_EINVAL;
+  if (b_up == nullptr && tokens > 0 && n > 0 && dim_a1 > 0 && z > 0) return B200GMM_EINVAL;
+  if (b_up == nullptr || dim_a1 == 0)  // nothing to multiply: silu(0) * 0 = 0, the plain path's zeros
+    return run_impl(a, b_gate, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
+                    workspace_bytes, device_status, cuda_stream, row_dest);
+  return run_impl(a, b_gate, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
+                  workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, b_up);
 }
 
 int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* batch_sizes,

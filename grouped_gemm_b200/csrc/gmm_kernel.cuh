@@ -157,15 +157,21 @@ struct TileWalker {
   }
 };
 
-template <int MODE, int CTAS, bool GATHER = false>
+template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
 __global__ void __launch_bounds__(GATHER ? gather_threads<CTAS>() : kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-           const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
+           const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
            const int64_t* __restrict__ batch_sizes, const Problem p,
            uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest,
            const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
            const int64_t a_src_rows) {
   static_assert(!GATHER || MODE != kTN, "the gathered operand is the row-major a of a forward or dgrad product");
+  static_assert(!SWIGLU || MODE != kTN, "the gated product is a forward product");
+  // SWIGLU: two right operands of n columns each, b (gate) and b2 (up).  The
+  // schedule runs over 2n virtual columns, 256 per tile: accumulator columns
+  // [0,128) are a @ b[:, c0 .. c0+128), columns [128,256) are a @ b2[:, c0 ..
+  // c0+128) with c0 = col0 / 2, and the epilogue writes the 128 output columns
+  // silu(gate) * up.
   using G = Geometry<CTAS>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
@@ -189,6 +195,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
+      if (SWIGLU) ptx::prefetch_tensormap(&map_b2);
       ptx::prefetch_tensormap(&map_c);
       for (int s = 0; s < kStages; ++s) {
         // the producer's expect_tx arrival, plus one arrival by the gather warp that owns
@@ -286,10 +293,19 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               if (!GATHER) ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
-                ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, k0, t.expert);
+                if (SWIGLU)
+                  ptx::tma_load_3d(sb + j * kBoxBytes, j < 2 ? &map_b : &map_b2, local_bar,
+                                   t.col0 / 2 + (j & 1) * 64, k0, t.expert);
+                else
+                  ptx::tma_load_3d(sb + j * kBoxBytes, &map_b, local_bar, t.col0 + j * 64, k0, t.expert);
             } else if (MODE == kNT) {
               if (!GATHER) ptx::tma_load_2d(sa, &map_a, local_bar, k0, t.row0);
-              ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0, t.expert);
+              if (SWIGLU) {  // the maps' boxes are 128 rows of b high
+                ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0 / 2, t.expert);
+                ptx::tma_load_3d(sb + G::kBBytes / 2, &map_b2, local_bar, k0, t.col0 / 2, t.expert);
+              } else {
+                ptx::tma_load_3d(sb, &map_b, local_bar, k0, t.col0, t.expert);
+              }
             } else {
               const int r0 = t.k_row0 + k0;
 #pragma unroll
@@ -309,11 +325,16 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               if (!GATHER) ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
-                ptx::tma_load_3d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, k0,
-                                      t.expert);
+                if (SWIGLU)  // the leader stages the gate columns, its peer the up columns
+                  ptx::tma_load_3d_pair(sb + j * kBoxBytes, leader ? &map_b : &map_b2, bar,
+                                        t.col0 / 2 + j * 64, k0, t.expert);
+                else
+                  ptx::tma_load_3d_pair(sb + j * kBoxBytes, &map_b, bar, t.col0 + col_off + j * 64, k0,
+                                        t.expert);
             } else if (MODE == kNT) {
               if (!GATHER) ptx::tma_load_2d_pair(sa, &map_a, bar, k0, t.row0 + row_off);
-              ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
+              if (SWIGLU) ptx::tma_load_3d_pair(sb, leader ? &map_b : &map_b2, bar, k0, t.col0 / 2, t.expert);
+              else ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
             } else {
               const int r0 = t.k_row0 + k0;
 #pragma unroll
@@ -545,10 +566,13 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const bool scatter = (MODE != kTN) && (row_dest != nullptr);
       const bool warp_full = !p.direct_store && !scatter && (row_off + q * 32 + 31) < t.valid_rows;
       const int64_t out_row0 = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0) : int64_t(t.row0);
-      __nv_bfloat16* crow = c + (out_row0 + r) * p.n + t.col0;
-      if (scatter && row_ok) crow = reinterpret_cast<__nv_bfloat16*>(row_dest[out_row0 + r]) + t.col0;
+      // Output geometry: the gated product writes half as many columns as it schedules.
+      const int64_t out_n = SWIGLU ? (p.n >> 1) : p.n;
+      const int out_col0 = SWIGLU ? (t.col0 >> 1) : t.col0;
+      __nv_bfloat16* crow = c + (out_row0 + r) * out_n + out_col0;
+      if (scatter && row_ok) crow = reinterpret_cast<__nv_bfloat16*>(row_dest[out_row0 + r]) + out_col0;
       const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp
-      const int cols_left = static_cast<int>(p.n) - t.col0;  // multiple of 8
+      const int cols_left = static_cast<int>(out_n) - out_col0;  // multiple of 8
       uint32_t va[32], vb[32];
       if (nkb == 0) {
         // Empty wgrad expert: its block of the output is zeros, same store path.
@@ -563,6 +587,35 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       ++it;
       if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[ab]), aph, abort_flag)) { ok = false; break; }
       ptx::tc_fence_after_sync();
+      if (SWIGLU) {
+        // This warp's 64 of the tile's 128 output columns: gate from accumulator
+        // columns [64 half, +64), up from the same columns of the second half.
+        const uint32_t tg = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN + half * 64;
+#pragma unroll 1
+        for (int ch = 0; ch < 2; ++ch) {
+          ptx::tmem_ld_32x32(tg + ch * 32, va);
+          ptx::tmem_ld_32x32(tg + kBlockN / 2 + ch * 32, vb);
+          ptx::tmem_ld_wait();
+          if (ch == 1) {
+            // Every column has been read: hand the accumulator back before the last stores.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
+              if (kPair) ptx::mbar_arrive_cluster(ptx::mapa(te_bar, 0));
+              else ptx::mbar_arrive(te_bar);
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float g = __uint_as_float(va[i]);
+            const float u = __uint_as_float(vb[i]);
+            va[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * u);  // silu(g) * u
+          }
+          emit(va, half * 64 + ch * 32, warp_full, row_ok, crow, cols_left, tile_row, out_col0);
+        }
+        continue;
+      }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN + col_base;
       ptx::tmem_ld_32x32(taddr, va);
 #pragma unroll 1

@@ -177,6 +177,25 @@ int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index,
                        uint32_t* device_status, void* cuda_stream);
 
 /*
+ * Gated forward product of a SwiGLU expert layer in one kernel:
+ *   c[rows_i, :] = silu(a[rows_i, :] @ b_gate[i]) * (a[rows_i, :] @ b_up[i])
+ * with silu(x) = x / (1 + exp(-x)).  b_gate and b_up have the shape b has in
+ * b200gmm_run with trans_a = 0 ([z, k, n], or [z, n, k] with trans_b); c is
+ * bf16 [tokens, n].  Both products accumulate in fp32 in one 256-column
+ * accumulator (128 gate columns, 128 up columns); the epilogue applies the gate
+ * to the fp32 values and rounds once, so neither product is written to memory.
+ * If row_dest is non-NULL the rows go to the addresses row_dest[i] as in
+ * b200gmm_run_scatter (c may then be NULL).
+ * The reference has no counterpart: its callers run gmm twice (or once on
+ * concatenated weights) and apply the activation in a separate kernel.
+ */
+int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void* c,
+                       const int64_t* row_dest, const int64_t* batch_sizes,
+                       int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1,
+                       int64_t n, int trans_b, void* workspace, size_t workspace_bytes,
+                       uint32_t* device_status, void* cuda_stream);
+
+/*
  * Row exchange for expert parallelism: copy `n_items` rows of `row_bytes` bytes
  * (a multiple of 16) from `src` on this GPU into rows of buffers that may live
  * on other GPUs.  Item i reads row src_row[i] of `src` (row i when src_row is

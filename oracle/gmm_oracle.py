@@ -95,6 +95,16 @@ def gmm(a, b, batch_sizes, trans_a=False, trans_b=False, c=None, accumulate_dtyp
     return out
 
 
+def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False):
+    """``silu(gmm(a, b_gate)) * gmm(a, b_up)`` with both products and the gate in
+    fp32 and one rounding to a's dtype at the end.  The reference has no such
+    operator; this composes its gmm semantics (the loop above) with
+    ``torch.nn.functional.silu`` to check the fused kernel."""
+    gate = gmm(a.float(), b_gate.float(), batch_sizes, trans_b=trans_b)
+    up = gmm(a.float(), b_up.float(), batch_sizes, trans_b=trans_b)
+    return (torch.nn.functional.silu(gate) * up).to(a.dtype)
+
+
 def gmm_backward(a, b, batch_sizes, grad, trans_b=False):
     """Gradients of ``gmm(a, b, batch_sizes, trans_b)`` for upstream ``grad``,
     with the operand choice of GroupedGemm.backward (grouped_gemm/ops.py:14-29):

@@ -63,3 +63,14 @@ def test_no_cpu_fallback():
     """CPU tensors are refused, not computed some other way."""
     with pytest.raises(RuntimeError):
         ops.gmm(_t(8, 16), _t(2, 16, 24), torch.tensor([4, 4]))
+
+
+def test_fused_entry_points_refuse_cpu_tensors():
+    """gmm_scatter / gmm_gather / gmm_swiglu have no CPU path either."""
+    a, b, bs = _t(8, 16), _t(2, 16, 24), torch.tensor([4, 4])
+    with pytest.raises(RuntimeError):
+        backend.gmm_swiglu(a, b, b.clone(), bs)
+    with pytest.raises(RuntimeError):
+        backend.gmm_gather(a, torch.arange(8), b, bs)
+    with pytest.raises(RuntimeError):
+        backend.gmm_scatter(a, b, bs, _t(8, 24), torch.arange(8))

@@ -573,6 +573,48 @@ def test_gmm_gather_row_index_out_of_range_reads_zeros(gg):
     assert torch.equal(got, want)
 
 
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("sizes,k,n", [
+    ([128, 128, 128, 128], 128, 128),            # whole tiles
+    ([300, 0, 5, 700, 129, 64, 1, 513], 200, 328),  # ragged rows, k tail, n not a multiple of 128
+    ([1000, 24], 512, 72),                        # a single narrow column tile
+    ([0, 0, 3], 64, 1040),
+])
+def test_gmm_swiglu_matches_the_oracle(gg, trans_b, sizes, k, n):
+    """silu(a @ b_gate) * (a @ b_up) from one kernel against the fp32 CPU
+    composition, and against the two-launch composition on the GPU."""
+    torch.manual_seed(16)
+    T, z = sum(sizes), len(sizes)
+    a = torch.randn(T, k, device="cuda").bfloat16()
+    shape = (z, n, k) if trans_b else (z, k, n)
+    bg = (torch.randn(*shape, device="cuda") * 0.1).bfloat16()
+    bu = (torch.randn(*shape, device="cuda") * 0.1).bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    got = gg.backend.gmm_swiglu(a, bg, bu, bs, trans_b=trans_b)
+    want = gmm_oracle.gmm_swiglu(a.cpu(), bg.cpu(), bu.cpu(), bs.cpu(), trans_b=trans_b)
+    util.assert_close(got, want, what="swiglu")
+    two = torch.nn.functional.silu(gg.backend.gmm(a, bg, bs, trans_b=trans_b).float()) \
+        * gg.backend.gmm(a, bu, bs, trans_b=trans_b).float()
+    util.assert_close(got, two, rtol=2e-2, atol=2e-2, what="swiglu vs two launches")
+    assert gg.backend.device_status() == 0
+
+
+def test_gmm_swiglu_many_tiles(gg):
+    """More tiles than CTAs, several k-blocks: both accumulator buffers in use."""
+    torch.manual_seed(17)
+    sizes = [1500, 0, 3000, 37, 4100, 900, 2, 1025]
+    T, k, n = sum(sizes), 1024, 1536
+    a = torch.randn(T, k, device="cuda").bfloat16()
+    bg = (torch.randn(len(sizes), k, n, device="cuda") * 0.05).bfloat16()
+    bu = (torch.randn(len(sizes), k, n, device="cuda") * 0.05).bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    c = torch.full((T + 3, n), 7.0, device="cuda", dtype=torch.bfloat16)
+    got = gg.backend.gmm_swiglu(a, bg, bu, bs, c=c[:T])
+    want = gmm_oracle.gmm_swiglu(a.cpu(), bg.cpu(), bu.cpu(), bs.cpu())
+    util.assert_close(got, want, what="swiglu")
+    assert bool((c[T:] == 7.0).all())
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""

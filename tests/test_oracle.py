@@ -111,3 +111,19 @@ def test_torch_oracle_equals_c_oracle_bitwise(trans_a, trans_b):
                         int(trans_a), int(trans_b))
     want = gmm_oracle.gmm(a, b, torch.from_numpy(bs), trans_a=trans_a, trans_b=trans_b)
     util.assert_close(c, want, rtol=2 ** -7, atol=1e-3, what="C vs torch oracle")
+
+
+def test_swiglu_composition():
+    """gmm_swiglu = silu(gate product) * up product, per expert, fp32 inside."""
+    torch.manual_seed(3)
+    a = torch.randn(10, 16).bfloat16()
+    bg, bu = torch.randn(2, 16, 8).bfloat16(), torch.randn(2, 16, 8).bfloat16()
+    got = gmm_oracle.gmm_swiglu(a, bg, bu, torch.tensor([4, 6]))
+    want = torch.empty(10, 8)
+    for i, (s0, s1) in enumerate([(0, 4), (4, 10)]):
+        gate = a[s0:s1].float() @ bg[i].float()
+        want[s0:s1] = gate / (1 + torch.exp(-gate)) * (a[s0:s1].float() @ bu[i].float())
+    assert torch.equal(got, want.bfloat16())
+    got_t = gmm_oracle.gmm_swiglu(a, bg.transpose(1, 2).contiguous(), bu.transpose(1, 2).contiguous(),
+                                  torch.tensor([4, 6]), trans_b=True)
+    assert torch.equal(got_t, got)
