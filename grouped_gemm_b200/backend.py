@@ -39,7 +39,7 @@ def gmm(a, b, batch_sizes, trans_a=False, trans_b=False, c=None):
     return out
 
 
-def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False):
+def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False, row_weight=None, accumulate=False):
     """``gmm`` with the un-sort fused into the kernel: row ``i`` of the grouped
     result is written to ``out[row_index[i]]`` instead of ``c[i]`` (no
     counterpart in the reference, whose callers un-permute ``c`` themselves).
@@ -47,7 +47,14 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False):
     ``a`` [T, k] holds the rows sorted by expert as for ``gmm``; ``out`` is a
     contiguous bf16 [R, n] tensor on the same device, ``row_index`` int64 [T] with
     values in [0, R).  Rows of ``out`` that no index names are left alone; if two
-    indices coincide the later write wins in no defined order.  Returns ``out``."""
+    indices coincide the later write wins in no defined order.  Returns ``out``.
+
+    ``row_weight`` (float32 [T], optional) multiplies row ``i`` in fp32 before the
+    rounding to bf16; ``accumulate=True`` adds the rows to ``out`` instead of
+    overwriting it, so that with top-k routing (k rows per token, all with the
+    same index) one call on a zeroed ``out`` leaves the weighted sum.  The order
+    of the additions to one row is not defined (last-bit differences between
+    runs)."""
     assert a.ndim == 2 and b.ndim == 3 and batch_sizes.ndim == 1 and out.ndim == 2 and row_index.ndim == 1
     n = b.shape[1] if trans_b else b.shape[2]
     k = b.shape[2] if trans_b else b.shape[1]
@@ -61,6 +68,9 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False):
         raise RuntimeError("gmm_scatter: a, b and out must be contiguous")
     if batch_sizes.dtype != torch.int64:
         raise RuntimeError("gmm_scatter: batch_sizes must be int64")
+    if row_weight is not None and not (row_weight.is_cuda and row_weight.dtype == torch.float32
+                                       and row_weight.shape == (a.shape[0],) and row_weight.is_contiguous()):
+        raise RuntimeError("gmm_scatter: row_weight must be a contiguous float32 CUDA tensor [T]")
     lib = _capi.load()
     z = batch_sizes.shape[0]
     with torch.cuda.device(a.device):
@@ -68,10 +78,18 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False):
         ws_bytes = _capi.workspace_bytes(z)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
         bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
-        rc = lib.b200gmm_run_scatter(
-            a.data_ptr(), b.data_ptr(), dest.data_ptr(), bs.data_ptr(), 1 if bs.is_cuda else 0, z,
-            a.shape[0], a.shape[1], n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
-            backend.device_status(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
+        status = backend.device_status(a.device).data_ptr()
+        stream = torch.cuda.current_stream(a.device).cuda_stream
+        if row_weight is None and not accumulate:
+            rc = lib.b200gmm_run_scatter(
+                a.data_ptr(), b.data_ptr(), dest.data_ptr(), bs.data_ptr(), 1 if bs.is_cuda else 0, z,
+                a.shape[0], a.shape[1], n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes, status, stream)
+        else:
+            rc = lib.b200gmm_run_combine(
+                a.data_ptr(), b.data_ptr(), dest.data_ptr(),
+                None if row_weight is None else row_weight.data_ptr(), 1 if accumulate else 0,
+                bs.data_ptr(), 1 if bs.is_cuda else 0, z,
+                a.shape[0], a.shape[1], n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes, status, stream)
     _capi.check(rc, "b200gmm_run_scatter")
     return out
 

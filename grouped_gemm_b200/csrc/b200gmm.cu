@@ -75,7 +75,8 @@ template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
 cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
                        const CUtensorMap& map_b2, const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
                        CUtensorMap* slots, const int64_t* row_dest, const int32_t* a_rows = nullptr,
-                       const __nv_bfloat16* a_src = nullptr, int64_t a_src_rows = 0) {
+                       const __nv_bfloat16* a_src = nullptr, int64_t a_src_rows = 0,
+                       const float* row_scale = nullptr, int reduce_add = 0) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(GATHER ? gather_threads<CTAS>() : kThreads);
@@ -89,7 +90,7 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, map_a, map_b, map_b2, map_c, c, bs, p, status, slots,
-                            row_dest, a_rows, a_src, a_src_rows);
+                            row_dest, a_rows, a_src, a_src_rows, row_scale, reduce_add);
 }
 
 template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
@@ -283,7 +284,9 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
              int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
              uint32_t* device_status, void* cuda_stream, const int64_t* row_dest,
-             const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr) {
+             const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr,
+             const float* row_scale = nullptr, int reduce_add = 0) {
+  if ((row_scale != nullptr || reduce_add) && row_dest == nullptr) return B200GMM_EINVAL;
   if (a_rows != nullptr && (trans_a || dim_a1 == 0 || a_source_rows <= 0)) return B200GMM_EINVAL;
   // b2 != nullptr: gated product silu(a @ b) * (a @ b2); n counts the columns of
   // each of b, b2 and c, the schedule runs over 2n virtual columns.
@@ -403,28 +406,28 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   const int grid = max_grid < kMaxCtas ? max_grid : kMaxCtas;
   if (gather) {
     if (ctas == 2) {
-      if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
-      else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
+      else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
     } else {
-      if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
-      else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows);
+      if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
+      else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
     }
   } else if (swiglu) {
     if (ctas == 2) {
-      if (p.mode == kNN) err = launch_gmm<kNN, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-      else err = launch_gmm<kNT, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+      if (p.mode == kNN) err = launch_gmm<kNN, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+      else err = launch_gmm<kNT, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
     } else {
-      if (p.mode == kNN) err = launch_gmm<kNN, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-      else err = launch_gmm<kNT, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+      if (p.mode == kNN) err = launch_gmm<kNN, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+      else err = launch_gmm<kNT, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
     }
   } else if (ctas == 2) {
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
   } else {
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest);
+    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
   }
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
@@ -453,6 +456,20 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest, c
   if (row_dest == nullptr) return B200GMM_EINVAL;
   return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
                   workspace, workspace_bytes, device_status, cuda_stream, row_dest);
+}
+
+int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest, const float* row_weight,
+                        int accumulate, const int64_t* batch_sizes, int batch_sizes_on_device, int z,
+                        int64_t tokens, int64_t dim_a1, int64_t n, int trans_b, void* workspace,
+                        size_t workspace_bytes, uint32_t* device_status, void* cuda_stream) {
+  if (row_dest == nullptr) return B200GMM_EINVAL;
+  if (row_weight != nullptr && (reinterpret_cast<uintptr_t>(row_weight) & 3)) return B200GMM_EALIGN;
+  // k == 0 would take the zero-fill shortcut of the shared body, which writes c;
+  // a combine has no c, and adding zeros changes nothing.
+  if (dim_a1 == 0) return accumulate ? B200GMM_OK : B200GMM_EINVAL;
+  return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
+                  workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr,
+                  row_weight, accumulate ? 1 : 0);
 }
 
 int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index, const void* b, void* c,

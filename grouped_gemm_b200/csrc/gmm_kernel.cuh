@@ -164,7 +164,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
            const int64_t* __restrict__ batch_sizes, const Problem p,
            uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest,
            const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
-           const int64_t a_src_rows) {
+           const int64_t a_src_rows, const float* __restrict__ row_scale, const int reduce_add) {
   static_assert(!GATHER || MODE != kTN, "the gathered operand is the row-major a of a forward or dgrad product");
   static_assert(!SWIGLU || MODE != kTN, "the gated product is a forward product");
   // SWIGLU: two right operands of n columns each, b (gate) and b2 (up).  The
@@ -542,7 +542,9 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                          : "memory");
           ptx::fence_proxy_async_smem();
           const int left = cols_left - col;
-          ptx::bulk_store_1d(crow + col, row_addr, left < 32 ? uint32_t(left) * 2u : 64u);
+          const uint32_t bytes = left < 32 ? uint32_t(left) * 2u : 64u;
+          if (reduce_add) ptx::bulk_reduce_add_bf16_1d(crow + col, row_addr, bytes);
+          else ptx::bulk_store_1d(crow + col, row_addr, bytes);
           ptx::bulk_commit_group();
         }
         ++stores;
@@ -573,6 +575,13 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       if (scatter && row_ok) crow = reinterpret_cast<__nv_bfloat16*>(row_dest[out_row0 + r]) + out_col0;
       const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp
       const int cols_left = static_cast<int>(out_n) - out_col0;  // multiple of 8
+      // Scatter mode with per-row weights (the router's top-k weight of this row).
+      const bool scaled = scatter && row_scale != nullptr;
+      const float row_w = (scaled && row_ok) ? row_scale[out_row0 + r] : 1.0f;
+      auto scale = [&](uint32_t (&v)[32]) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * row_w);
+      };
       uint32_t va[32], vb[32];
       if (nkb == 0) {
         // Empty wgrad expert: its block of the output is zeros, same store path.
@@ -612,6 +621,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             const float u = __uint_as_float(vb[i]);
             va[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * u);  // silu(g) * u
           }
+          if (scaled) scale(va);
           emit(va, half * 64 + ch * 32, warp_full, row_ok, crow, cols_left, tile_row, out_col0);
         }
         continue;
@@ -622,6 +632,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       for (int ch = 0; ch < kBlockN / 64; ch += 2) {
         ptx::tmem_ld_wait();
         ptx::tmem_ld_32x32(taddr + (ch + 1) * 32, vb);
+        if (scaled) scale(va);
         emit(va, col_base + ch * 32, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
         ptx::tmem_ld_wait();
         if (ch + 2 < kBlockN / 64) {
@@ -636,6 +647,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             else ptx::mbar_arrive(te_bar);
           }
         }
+        if (scaled) scale(vb);
         emit(vb, col_base + (ch + 1) * 32, warp_full, row_ok, crow, cols_left, tile_row, t.col0);
       }
     }

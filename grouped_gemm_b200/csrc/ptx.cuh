@@ -141,6 +141,15 @@ __device__ __forceinline__ void bulk_store_1d(void* dst, uint32_t src, uint32_t 
                : "l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
                : "memory");
 }
+// Same copy, but the bf16 values are ADDED to those at the destination (element-wise
+// reduction done by the memory system; the order of concurrent additions to
+// one element is not defined).
+__device__ __forceinline__ void bulk_reduce_add_bf16_1d(void* dst, uint32_t src, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.bf16 [%0], [%1], %2;"
+               :
+               : "l"(reinterpret_cast<uint64_t>(dst)), "r"(src), "r"(bytes)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

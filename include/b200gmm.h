@@ -154,6 +154,26 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
                         uint32_t* device_status, void* cuda_stream);
 
 /*
+ * b200gmm_run_scatter with the router's weights and the top-k sum folded in:
+ * row i of the product is multiplied by row_weight[i] (device float [tokens];
+ * NULL = 1) in fp32 before it is rounded to bf16, and, if accumulate is
+ * non-zero, ADDED to the bf16 row at row_dest[i] instead of overwriting it
+ * (bulk reduce-add copies).  With top-k routing the k rows of one token, which
+ * belong to k experts, carry the same destination: the caller zeroes the output,
+ * one call sums all contributions.  The additions of different rows to one
+ * destination happen in no defined order, each rounding to bf16, so results can
+ * differ in the last bit from run to run.  Destinations may be peer memory, as
+ * in b200gmm_run_scatter.  The reference has no counterpart: its callers
+ * un-sort, weight and sum in kernels of their own.
+ */
+int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest,
+                        const float* row_weight, int accumulate,
+                        const int64_t* batch_sizes, int batch_sizes_on_device, int z,
+                        int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
+                        void* workspace, size_t workspace_bytes,
+                        uint32_t* device_status, void* cuda_stream);
+
+/*
  * b200gmm_run (trans_a = 0 only) with the caller's sort-by-expert fused into the
  * operand load: row i of the grouped left operand is row row_index[i] of `x`
  * (bf16 [x_rows, dim_a1], contiguous; row_index: device int32 [tokens], values in

@@ -615,6 +615,39 @@ def test_gmm_swiglu_many_tiles(gg):
     assert bool((c[T:] == 7.0).all())
 
 
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_gmm_scatter_weighted_topk_combine(gg, trans_b):
+    """Top-2 routing: every token has two rows (two experts); one call with
+    row_weight and accumulate leaves sum_k w_k * (x @ b[e_k]) in the token's row."""
+    torch.manual_seed(18)
+    tokens, z, k, n, topk = 700, 6, 200, 328, 2
+    x = torch.randn(tokens, k, device="cuda").bfloat16()
+    b = (torch.randn(z, n, k, device="cuda") if trans_b else torch.randn(z, k, n, device="cuda")).bfloat16() * 0.1
+    experts = torch.stack([torch.randperm(z, device="cuda")[:topk] for _ in range(tokens)])  # [tokens, 2] distinct
+    weights = torch.rand(tokens, topk, device="cuda")
+    flat_e = experts.reshape(-1)
+    order = torch.argsort(flat_e, stable=True)
+    token_of_row = (order // topk)
+    a = x[token_of_row].contiguous()
+    w = weights.reshape(-1)[order].contiguous()
+    bs = torch.bincount(flat_e, minlength=z).to(torch.int64)
+    out = torch.zeros(tokens + 2, n, device="cuda", dtype=torch.bfloat16)
+    gg.backend.gmm_scatter(a, b, bs, out, token_of_row, trans_b=trans_b, row_weight=w, accumulate=True)
+    rows = gmm_oracle.gmm(a.cpu().float(), b.cpu().float(), bs.cpu(), trans_b=trans_b)   # fp32 rows
+    want = torch.zeros(tokens + 2, n)
+    want.index_add_(0, token_of_row.cpu(), rows * w.cpu()[:, None])
+    util.assert_close(out, want, rtol=2e-2, atol=2e-2, what="weighted top-k combine")
+    assert bool((out[tokens:] == 0).all())
+    # weights without accumulation: plain scatter of w * row (distinct destinations)
+    out2 = torch.full((a.shape[0], n), 3.0, device="cuda", dtype=torch.bfloat16)
+    perm = torch.randperm(a.shape[0], device="cuda")
+    gg.backend.gmm_scatter(a, b, bs, out2, perm, trans_b=trans_b, row_weight=w)
+    want2 = torch.empty(a.shape[0], n)
+    want2[perm.cpu()] = rows * w.cpu()[:, None]
+    util.assert_close(out2, want2, what="weighted scatter")
+    assert gg.backend.device_status() == 0
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
