@@ -381,6 +381,10 @@ def run_single(args):
     grad = torch.randn(rows, n, device=dev, generator=g).bfloat16()
     e2e = e2e_single(backend, a, b, grad, bs, flops_pass, max(4, min(args.steps, 8)))
 
+    fused = None
+    if args.fused:
+        del a, b, grad
+        fused = fused_neighbours(backend, dev, bs)
     scaling_base = ep_value_single(args.steps, dev) if args.scaling_base else None
     baseline = cpu_baseline() if not args.no_cpu_baseline else None
 
@@ -395,6 +399,8 @@ def run_single(args):
     }
     if scaling_base is not None:
         line["scaling_base"] = scaling_base
+    if fused is not None:
+        line["fused_neighbours"] = fused
     print(json.dumps(line), flush=True)
 
 
@@ -402,10 +408,77 @@ def run_single(args):
 # benchmark's size, from the ncu captures summarised in
 # profiles/gmm_kernel_mixtral_ncu_full.md (full-size launches, so no scaling).
 TRAFFIC_BYTES = {
-    "gmm_kernel<NN>": 4.405e9 + 0.928e9,
-    "gmm_kernel<NT>": 9.187e9 + 0.267e9,
-    "gmm_kernel<TN>": 6.635e9 + 0.911e9,
+    "gmm_kernel<NN>": 4.133e9 + 0.932e9,
+    "gmm_kernel<NT>": 8.610e9 + 0.267e9,
+    "gmm_kernel<TN>": 6.367e9 + 0.918e9,
 }
+
+
+def fused_neighbours(backend, dev, bs, rounds=6):
+    """The caller-side passes either side of gmm, fused into the kernel, each timed
+    against the same work done with separate torch kernels (Mixtral shapes; rounds
+    interleaved so that both sides see the same clocks; median and min in ms)."""
+    z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["k"], MIXTRAL["n"]
+    g = torch.Generator(device=dev).manual_seed(5)
+    F = torch.nn.functional
+
+    def compare(cases):
+        for _, fn in cases:
+            fn()
+        acc = {name: [] for name, _ in cases}
+        for _ in range(rounds):
+            for name, fn in cases:
+                fn()
+                acc[name].append(time_loop(fn, 5))
+        return {name: {"median_ms": sorted(v)[len(v) // 2], "min_ms": min(v)} for name, v in acc.items()}
+
+    out = {"workload": "mixtral shapes, z=8, 32768 rows; up-projection k=4096 n=14336, down-projection k=14336 n=4096"}
+    # sort-by-expert fused into the A-tile load
+    tokens = rows // 2
+    x = torch.randn(tokens, k, device=dev, generator=g).bfloat16()
+    idx = torch.randint(0, tokens, (rows,), device=dev, generator=g)
+    b_gate = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+    a = x.index_select(0, idx)
+    out["gather"] = compare((
+        ("gmm_gather", lambda: backend.gmm_gather(x, idx, b_gate, bs, c=c)),
+        ("index_select + gmm", lambda: backend.gmm(x.index_select(0, idx), b_gate, bs, c=c)),
+        ("gmm on rows already sorted", lambda: backend.gmm(a, b_gate, bs, c=c))))
+    # gate and up products with the activation in the epilogue
+    b_up = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+    h1 = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+
+    def two_launches():
+        backend.gmm(a, b_gate, bs, c=c)
+        backend.gmm(a, b_up, bs, c=h1)
+        return F.silu(c) * h1
+
+    out["swiglu"] = compare((
+        ("gmm_swiglu", lambda: backend.gmm_swiglu(a, b_gate, b_up, bs, c=c)),
+        ("2 gmm + silu * mul", two_launches)))
+    del b_gate, b_up, h1, x, a
+    # weighted top-2 combine in the epilogue of the down-projection
+    a2 = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+    b_down = (torch.randn(z, n, k, device=dev, generator=g) * 0.02).bfloat16()
+    token_of_row = torch.randint(0, tokens, (rows,), device=dev, generator=g)
+    weight = torch.rand(rows, device=dev, generator=g)
+    y = torch.empty(rows, k, device=dev, dtype=torch.bfloat16)
+    result = torch.zeros(tokens, k, device=dev, dtype=torch.bfloat16)
+
+    def fused_combine():
+        result.zero_()
+        backend.gmm_scatter(a2, b_down, bs, result, token_of_row, row_weight=weight, accumulate=True)
+
+    def separate_combine():
+        backend.gmm(a2, b_down, bs, c=y)
+        result.zero_()
+        result.index_add_(0, token_of_row, (y.float() * weight[:, None]).bfloat16())
+
+    out["combine"] = compare((
+        ("gmm_scatter(row_weight, accumulate)", fused_combine),
+        ("gmm + weight + index_add_", separate_combine),
+        ("gmm alone", lambda: backend.gmm(a2, b_down, bs, c=y))))
+    return out
 
 
 def down_projection(backend, dev, bs, iters):
@@ -750,6 +823,8 @@ def main():
                     help="multi-GPU runs: combine with separate push kernels instead of from the GEMM epilogues")
     ap.add_argument("--no-scaling-base", action="store_true",
                     help="multi-GPU runs: skip timing the same workload on rank 0's GPU alone")
+    ap.add_argument("--fused", action="store_true",
+                    help="also time gmm_gather, gmm_swiglu and the weighted combine against separate torch kernels")
     ap.add_argument("--scaling-base", action="store_true",
                     help="also time the multi-GPU workload on this one GPU (strong-scaling denominator)")
     args = ap.parse_args()
