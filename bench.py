@@ -791,6 +791,18 @@ def run_profile_case(args):
         b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
         c = torch.empty(rows, k, device=dev, dtype=torch.bfloat16)
         fn = lambda: backend.gmm(a, b, bs, trans_b=True, c=c)
+    elif args.profile == "gather":
+        x = torch.randn(rows // 2, k, device=dev, generator=g).bfloat16()
+        idx = torch.randint(0, rows // 2, (rows,), device=dev, generator=g)
+        b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+        c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: backend.gmm_gather(x, idx, b, bs, c=c)
+    elif args.profile == "swiglu":
+        a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+        b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+        b2 = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+        c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        fn = lambda: backend.gmm_swiglu(a, b, b2, bs, c=c)
     else:
         a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
         b = torch.randn(rows, n, device=dev, generator=g).bfloat16()
@@ -805,7 +817,7 @@ def run_profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", choices=["fwd", "dgrad", "wgrad"], default=None,
+    ap.add_argument("--profile", choices=["fwd", "dgrad", "wgrad", "gather", "swiglu"], default=None,
                     help="launch one pass of the Mixtral workload a few times and exit (for ncu)")
     ap.add_argument("--profile-launches", type=int, default=2)
     ap.add_argument("--profile-workload", choices=["mixtral", "fine"], default="mixtral")
