@@ -162,8 +162,9 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
  * belong to k experts, carry the same destination: the caller zeroes the output,
  * one call sums all contributions.  The additions of different rows to one
  * destination happen in no defined order, each rounding to bf16, so results can
- * differ in the last bit from run to run.  Destinations may be peer memory, as
- * in b200gmm_run_scatter.  The reference has no counterpart: its callers
+ * differ in the last bit from run to run.  Destinations in another GPU's memory
+ * have been exercised with the plain copies of b200gmm_run_scatter only, not
+ * with the reduce-add copies.  The reference has no counterpart: its callers
  * un-sort, weight and sum in kernels of their own.
  */
 int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest,
