@@ -583,8 +583,31 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * row_w);
       };
       uint32_t va[32], vb[32];
-      if (nkb == 0) {
-        // Empty wgrad expert: its block of the output is zeros, same store path.
+      if (MODE == kTN && nkb == 0) {  // (forward and dgrad tiles always have k > 0)
+        // Empty wgrad expert: its block of the output is zeros.
+        if (warp_full) {
+          // Zeros need staging once: every store of this tile reads the same buffer,
+          // so none of them waits for the one before.
+          if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<0>();
+          __syncwarp();
+          const uint32_t row_addr = my_out + uint32_t(lane) * 64u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(row_addr + (uint32_t(j) << 4)), "r"(0u)
+                         : "memory");
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+#pragma unroll 1
+            for (int ch = 0; ch < kBlockN / 64; ++ch) {
+              const int col = col_base + ch * 32;
+              if (col < cols_left) ptx::tma_store_2d(&map_c, my_out, t.col0 + col, tile_row);
+            }
+            ptx::bulk_commit_group();
+          }
+          ++stores;
+          continue;
+        }
 #pragma unroll
         for (int i = 0; i < 32; ++i) va[i] = 0u;
 #pragma unroll 1
