@@ -25,6 +25,16 @@
 //               third and shrinks a stage to 32 KiB, so six stages fit.  No TMA
 //               multicast is used anywhere.
 //
+// Optional template variants (forward / dgrad layouts only):
+//   GATHER      row i of A is row a_rows[i] of another tensor: one extra warp per
+//               ring stage fetches the rows with cp.async in place of the TMA box
+//               loads of A (B still comes by TMA);
+//   SWIGLU      two right operands; the accumulator holds 128 gate and 128 up
+//               columns and the epilogue writes silu(gate) * up.
+// and run-time options of the epilogue: rows scattered to addresses given per row
+// (row_dest), scaled per row (row_scale) and added to the destination instead of
+// stored (reduce_add).
+//
 // This replaces the CUTLASS GemmGrouped instantiations of the reference
 // (csrc/grouped_gemm.cu:38-81, :324-371), its argument-fill kernel
 // (csrc/fill_arguments.cuh:34-98) and the k==0 zero-fill kernels
