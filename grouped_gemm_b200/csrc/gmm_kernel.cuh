@@ -65,14 +65,19 @@ constexpr uint32_t kBoxBytes = 64 * kBlockK * 2;  // one 64-wide MN-major TMA bo
 constexpr int kMapSlots = 8;
 constexpr int kMaxCtas = 256;  // workspace is sized for this many CTAs
 
-template <int CTAS>
+// wgrad gives up one ring stage for a second epilogue staging buffer per warp: its
+// tiles can be a single k-block deep (few rows per expert, or none), and then the
+// kernel runs at the speed of its output stores.
+template <int CTAS, int MODE = kNN>
 struct Geometry {
-  static constexpr int kStages = (CTAS == 1) ? 4 : 6;
+  static constexpr int kStages = (MODE == kTN) ? ((CTAS == 1) ? 3 : 5) : ((CTAS == 1) ? 4 : 6);
+  static constexpr int kOutBufs = (MODE == kTN) ? 2 : 1;  // staging buffers per epilogue warp
   static constexpr int kBCols = kBlockN / CTAS;                 // B columns staged by one CTA
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;    // 16 KiB
   static constexpr uint32_t kBBytes = kBCols * kBlockK * 2;     // 32 or 16 KiB
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB either way
+  static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB (wgrad: 160 or 144 KiB)
+  static constexpr uint32_t kOutBytes = kEpilogueWarps * kOutBufs * 2048u;  // 16 KiB (wgrad: 32 KiB)
 };
 
 // The gather variant adds one warp per ring stage; each fetches the rows of A for
@@ -80,11 +85,12 @@ struct Geometry {
 template <int CTAS>
 constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS>::kStages; }
 
-// Epilogue staging: per epilogue warp one buffer of 32 rows x 32 bf16 columns
-// (64-byte rows, 64-byte swizzle), the source of its TMA stores.  A warp converts
-// its next chunk in registers while the previous store still reads the buffer.
+// Epilogue staging: per epilogue warp one buffer (wgrad: two, used in turn) of 32
+// rows x 32 bf16 columns (64-byte rows, 64-byte swizzle), the source of its TMA
+// stores.  A warp converts its next chunk in registers while the previous store
+// still reads the buffer.
 constexpr uint32_t kStageOutBytes = 32 * 32 * 2;                  // 2 KiB
-constexpr uint32_t kOutBytes = kEpilogueWarps * kStageOutBytes;   // 16 KiB
+static_assert(kStageOutBytes == 2048u, "Geometry::kOutBytes assumes 2 KiB buffers");
 
 struct __align__(8) SmemTail {
   uint64_t full[kMaxStages];
@@ -97,10 +103,14 @@ struct __align__(8) SmemTail {
   int tile_start[kMaxExperts + 1];
 };
 
+// One size for every instantiation: the largest layout (forward / dgrad).
 constexpr size_t kSmemBytes =
-    1024 /*alignment slack*/ + Geometry<1>::kRingBytes + kOutBytes + sizeof(SmemTail);
+    1024 /*alignment slack*/ + Geometry<1>::kRingBytes + Geometry<1>::kOutBytes + sizeof(SmemTail);
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
 static_assert(Geometry<1>::kRingBytes == Geometry<2>::kRingBytes, "both variants use the same ring size");
+static_assert(Geometry<1, kTN>::kRingBytes + Geometry<1, kTN>::kOutBytes <= Geometry<1>::kRingBytes + Geometry<1>::kOutBytes &&
+              Geometry<2, kTN>::kRingBytes + Geometry<2, kTN>::kOutBytes <= Geometry<1>::kRingBytes + Geometry<1>::kOutBytes,
+              "the wgrad layout must fit the common size");
 
 // Exclusive prefix sums of batch_sizes (rows) and of per-expert tile counts,
 // by one warp, 32 experts per step with a running carry.  Rows are clamped to
@@ -182,7 +192,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   // [0,128) are a @ b[:, c0 .. c0+128), columns [128,256) are a @ b2[:, c0 ..
   // c0+128) with c0 = col0 / 2, and the epilogue writes the 128 output columns
   // silu(gate) * up.
-  using G = Geometry<CTAS>;
+  using G = Geometry<CTAS, MODE>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
 
@@ -192,7 +202,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   uint8_t* smem = smem_raw + pad;  // 1024-byte aligned: required by the 128-byte swizzle
   const uint32_t stage_base = raw_addr + pad;
   const uint32_t out_base = stage_base + G::kRingBytes;
-  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + G::kRingBytes + kOutBytes);
+  SmemTail* tail = reinterpret_cast<SmemTail*>(smem + G::kRingBytes + G::kOutBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -490,12 +500,15 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
     const int col_base = half * (kBlockN / 2);
-    const uint32_t my_out = out_base + uint32_t(warp - 2) * kStageOutBytes;
+    const uint32_t my_out = out_base + uint32_t(warp - 2) * (kStageOutBytes * G::kOutBufs);
     TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
     Tile t;
     uint32_t it = 0;
     uint32_t stores = 0;  // TMA stores this warp has issued (lane 0's bulk groups)
     bool ok = true;
+    // Buffer for the next TMA store and the wait before it may be written: with two
+    // buffers the store before last read this one.
+    auto stage_buf = [&]() { return my_out + (G::kOutBufs == 2 ? (stores & 1u) * kStageOutBytes : 0u); };
 
     // One 32-column chunk `v` (fp32 bits) of this lane's row, starting at column
     // `col` of the tile: through the staging buffer and a TMA store when the
@@ -518,11 +531,12 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         o[j].w = *reinterpret_cast<uint32_t*>(&h);
       }
       if (warp_full) {
-        // The previous store read this buffer; it must be done reading.
-        if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<0>();
+        // The store that last read this buffer must be done reading.
+        const uint32_t buf = stage_buf();
+        if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<G::kOutBufs - 1>();
         __syncwarp();
         // 64-byte swizzle: 16-byte chunk index ^= (row / 2) % 4.
-        const uint32_t row_addr = my_out + uint32_t(lane) * 64u;
+        const uint32_t row_addr = buf + uint32_t(lane) * 64u;
         const uint32_t sw = (uint32_t(lane) >> 1) & 3u;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -534,7 +548,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_2d(&map_c, my_out, col0 + col, tile_row);
+          ptx::tma_store_2d(&map_c, buf, col0 + col, tile_row);
           ptx::bulk_commit_group();
         }
         ++stores;
@@ -598,9 +612,10 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         if (warp_full) {
           // Zeros need staging once: every store of this tile reads the same buffer,
           // so none of them waits for the one before.
-          if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<0>();
+          const uint32_t buf = stage_buf();
+          if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<G::kOutBufs - 1>();
           __syncwarp();
-          const uint32_t row_addr = my_out + uint32_t(lane) * 64u;
+          const uint32_t row_addr = buf + uint32_t(lane) * 64u;
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(row_addr + (uint32_t(j) << 4)), "r"(0u)
@@ -611,7 +626,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
 #pragma unroll 1
             for (int ch = 0; ch < kBlockN / 64; ++ch) {
               const int col = col_base + ch * 32;
-              if (col < cols_left) ptx::tma_store_2d(&map_c, my_out, t.col0 + col, tile_row);
+              if (col < cols_left) ptx::tma_store_2d(&map_c, buf, t.col0 + col, tile_row);
             }
             ptx::bulk_commit_group();
           }
