@@ -291,7 +291,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   // b2 != nullptr: gated product silu(a @ b) * (a @ b2); n counts the columns of
   // each of b, b2 and c, the schedule runs over 2n virtual columns.
   const bool swiglu = (b2 != nullptr);
-  if (swiglu && (trans_a || a_rows != nullptr || (reinterpret_cast<uintptr_t>(b2) & 15))) return B200GMM_EINVAL;
+  if (swiglu && (trans_a || a_rows != nullptr)) return B200GMM_EINVAL;
+  if (swiglu && (reinterpret_cast<uintptr_t>(b2) & 15)) return B200GMM_EALIGN;
   if (swiglu && (n % 8) != 0) return B200GMM_EALIGN;
   const int64_t n_out = n;
   if (swiglu) n = 2 * n;

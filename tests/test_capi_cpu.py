@@ -70,6 +70,33 @@ def test_run_with_no_work_is_ok_without_gpu():
     assert lib.b200gmm_run(None, None, None, bs.ctypes.data, 0, 4, 0, 128, 128, 0, 0, None, 0, None, None) == 0
 
 
+def test_fused_entry_points_reject_bad_arguments_before_cuda():
+    """Argument checks of the scatter / combine / gather / swiglu entry points
+    that return before any CUDA call (so they can run without a GPU)."""
+    lib = _capi.load()
+    bs = np.array([64, 64], dtype=np.int64)
+    dummy = np.zeros(64, dtype=np.int64).ctypes.data  # any non-null, 16-byte aligned address
+    # scatter and combine need a destination table
+    assert lib.b200gmm_run_scatter(dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_combine(dummy, dummy, None, None, 1, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    # combine: weights must be 4-byte aligned; k == 0 overwrite has nothing to write through
+    assert lib.b200gmm_run_combine(dummy, dummy, dummy, dummy + 2, 1, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -2
+    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 0, bs.ctypes.data, 0, 2, 128, 0, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 1, bs.ctypes.data, 0, 2, 128, 0, 64, 0, None, 0, None, None) == 0
+    # gather: row index table, a non-empty source below 2^31 rows, an output of some kind
+    assert lib.b200gmm_run_gather(dummy, 100, None, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 0, dummy, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 2 ** 31, dummy, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 100, dummy, dummy, None, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    # swiglu: both weight tensors, an output, column count a multiple of 8
+    assert lib.b200gmm_run_swiglu(dummy, dummy, None, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy, None, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 60, 0, None, 0, None, None) == -2
+    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy + 8, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -2
+    # the static-scratch entry point refuses more experts than its scratch holds
+    assert lib.b200gmm_run_static(dummy, dummy, dummy, bs.ctypes.data, 0, 257, 128, 64, 64, 0, 0, None, None) == -3
+
+
 def _schedule(sizes, tokens, d1, n, trans_a, trans_b, ctas=1):
     lib = _capi.load()
     bs = np.asarray(sizes, dtype=np.int64)
