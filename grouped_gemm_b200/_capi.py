@@ -47,6 +47,10 @@ SIGNATURES = {
         _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
+    "b200gmm_run_gather_wgrad": (_c.c_int, [
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+        _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64,
+        _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_run_swiglu": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,

@@ -148,6 +148,37 @@ def gmm_gather(x, row_index, b, batch_sizes, trans_b=False, c=None, out=None, ou
     return result
 
 
+def gmm_gather_wgrad(x, row_index, grad, batch_sizes, c=None):
+    """``gmm(x[row_index], grad, batch_sizes, trans_a=True)`` without materialising
+    ``x[row_index]``: the weight gradient of ``gmm_gather`` (no counterpart in the
+    reference).  ``x`` bf16 [R, k]; ``row_index`` integer [T]; ``grad`` bf16 [T, n]
+    grouped by expert; returns bf16 [z, k, n] (zeros for empty experts)."""
+    assert x.ndim == 2 and grad.ndim == 2 and batch_sizes.ndim == 1 and row_index.ndim == 1
+    if not (x.is_cuda and grad.is_cuda and row_index.is_cuda):
+        raise RuntimeError("gmm_gather_wgrad: x, grad and row_index must be CUDA tensors")
+    if not (x.dtype == grad.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
+        raise RuntimeError("gmm_gather_wgrad: x and grad must be bfloat16, batch_sizes int64")
+    tokens, n, k, z = grad.shape[0], grad.shape[1], x.shape[1], batch_sizes.shape[0]
+    if row_index.shape[0] != tokens or not (x.is_contiguous() and grad.is_contiguous()):
+        raise RuntimeError("gmm_gather_wgrad: shapes of x, row_index and grad do not fit together, or not contiguous")
+    if c is None:
+        c = torch.empty(z, k, n, device=x.device, dtype=x.dtype)
+    elif c.shape != (z, k, n) or c.dtype != torch.bfloat16 or not c.is_contiguous() or c.device != x.device:
+        raise RuntimeError("gmm_gather_wgrad: c must be contiguous bf16 [z, k, n] on x's device")
+    idx32 = row_index.to(torch.int32).contiguous()
+    lib = _capi.load()
+    with torch.cuda.device(x.device):
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
+        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        rc = lib.b200gmm_run_gather_wgrad(
+            x.data_ptr(), x.shape[0], idx32.data_ptr(), grad.data_ptr(), c.data_ptr(), bs.data_ptr(),
+            1 if bs.is_cuda else 0, z, tokens, k, n, ws.data_ptr(), ws_bytes,
+            backend.device_status(x.device).data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
+    _capi.check(rc, "b200gmm_run_gather_wgrad")
+    return c
+
+
 def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False, c=None):
     """``silu(gmm(a, b_gate)) * gmm(a, b_up)`` in one kernel: the gated first
     half of a SwiGLU expert layer (no counterpart in the reference, whose

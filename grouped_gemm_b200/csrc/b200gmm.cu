@@ -79,7 +79,7 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
                        const float* row_scale = nullptr, int reduce_add = 0) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
-  cfg.blockDim = dim3(GATHER ? gather_threads<CTAS>() : kThreads);
+  cfg.blockDim = dim3(GATHER ? gather_threads<CTAS, MODE>() : kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -120,6 +120,7 @@ int device_info(DeviceInfo** out) {
         set_smem_attr<kNT, 2>() != cudaSuccess || set_smem_attr<kTN, 2>() != cudaSuccess ||
         set_smem_attr<kNN, 1, true>() != cudaSuccess || set_smem_attr<kNT, 1, true>() != cudaSuccess ||
         set_smem_attr<kNN, 2, true>() != cudaSuccess || set_smem_attr<kNT, 2, true>() != cudaSuccess ||
+        set_smem_attr<kTN, 1, true>() != cudaSuccess || set_smem_attr<kTN, 2, true>() != cudaSuccess ||
         set_smem_attr<kNN, 1, false, true>() != cudaSuccess || set_smem_attr<kNT, 1, false, true>() != cudaSuccess ||
         set_smem_attr<kNN, 2, false, true>() != cudaSuccess || set_smem_attr<kNT, 2, false, true>() != cudaSuccess)
       return B200GMM_ECUDA;
@@ -287,7 +288,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr,
              const float* row_scale = nullptr, int reduce_add = 0) {
   if ((row_scale != nullptr || reduce_add) && row_dest == nullptr) return B200GMM_EINVAL;
-  if (a_rows != nullptr && (trans_a || dim_a1 == 0 || a_source_rows <= 0)) return B200GMM_EINVAL;
+  if (a_rows != nullptr && (dim_a1 == 0 || a_source_rows <= 0 || (trans_a && row_dest != nullptr)))
+    return B200GMM_EINVAL;
   // b2 != nullptr: gated product silu(a @ b) * (a @ b2); n counts the columns of
   // each of b, b2 and c, the schedule runs over 2n virtual columns.
   const bool swiglu = (b2 != nullptr);
@@ -383,8 +385,9 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     const uint64_t da[2] = {D1, T};
     const uint64_t db[2] = {N, T};
     const uint32_t bx[2] = {64, kBlockK};
-    if ((rc = encode_map(&map_a, a, 2, da, bx)) != 0 || (rc = encode_map(&map_b, b, 2, db, bx)) != 0)
-      return rc;
+    if ((rc = encode_map(&map_b, b, 2, db, bx)) != 0) return rc;
+    if (gather) map_a = map_b;
+    else if ((rc = encode_map(&map_a, a, 2, da, bx)) != 0) return rc;
   }
 
   if (!swiglu) map_b2 = map_b;  // unused by the kernel, but a valid map
@@ -408,9 +411,11 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   if (gather) {
     if (ctas == 2) {
       if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
+      else if (p.mode == kTN) err = launch_gmm<kTN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
       else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
     } else {
       if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
+      else if (p.mode == kTN) err = launch_gmm<kTN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
       else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
     }
   } else if (swiglu) {
@@ -481,6 +486,15 @@ int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index, 
   if (c == nullptr && row_dest == nullptr) return B200GMM_EINVAL;
   return run_impl(x, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
                   workspace_bytes, device_status, cuda_stream, row_dest, row_index, x_rows);
+}
+
+int b200gmm_run_gather_wgrad(const void* x, int64_t x_rows, const int32_t* row_index, const void* grad, void* c,
+                             const int64_t* batch_sizes, int batch_sizes_on_device, int z, int64_t tokens,
+                             int64_t dim_x1, int64_t n, void* workspace, size_t workspace_bytes,
+                             uint32_t* device_status, void* cuda_stream) {
+  if (row_index == nullptr || x_rows <= 0 || x_rows >= (int64_t(1) << 31)) return B200GMM_EINVAL;
+  return run_impl(x, grad, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_x1, n, 1, 0, workspace,
+                  workspace_bytes, device_status, cuda_stream, nullptr, row_index, x_rows);
 }
 
 int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void* c, const int64_t* row_dest,

@@ -25,12 +25,13 @@
 //               third and shrinks a stage to 32 KiB, so six stages fit.  No TMA
 //               multicast is used anywhere.
 //
-// Optional template variants (forward / dgrad layouts only):
+// Optional template variants:
 //   GATHER      row i of A is row a_rows[i] of another tensor: one extra warp per
 //               ring stage fetches the rows with cp.async in place of the TMA box
-//               loads of A (B still comes by TMA);
-//   SWIGLU      two right operands; the accumulator holds 128 gate and 128 up
-//               columns and the epilogue writes silu(gate) * up.
+//               loads of A (B still comes by TMA); also for wgrad, where the
+//               gathered rows are the contraction;
+//   SWIGLU      (forward / dgrad layouts) two right operands; the accumulator holds
+//               128 gate and 128 up columns and the epilogue writes silu(gate) * up.
 // and run-time options of the epilogue: rows scattered to addresses given per row
 // (row_dest), scaled per row (row_scale) and added to the destination instead of
 // stored (reduce_add).
@@ -82,8 +83,8 @@ struct Geometry {
 
 // The gather variant adds one warp per ring stage; each fetches the rows of A for
 // the k-blocks that land in its stage (512 threads for a CTA pair, 448 for one CTA).
-template <int CTAS>
-constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS>::kStages; }
+template <int CTAS, int MODE = kNN>
+constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS, MODE>::kStages; }
 
 // Epilogue staging: per epilogue warp one buffer (wgrad: two, used in turn) of 32
 // rows x 32 bf16 columns (64-byte rows, 64-byte swizzle), the source of its TMA
@@ -178,14 +179,13 @@ struct TileWalker {
 };
 
 template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
-__global__ void __launch_bounds__(GATHER ? gather_threads<CTAS>() : kThreads, 1)
+__global__ void __launch_bounds__(GATHER ? gather_threads<CTAS, MODE>() : kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
            const int64_t* __restrict__ batch_sizes, const Problem p,
            uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest,
            const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
            const int64_t a_src_rows, const float* __restrict__ row_scale, const int reduce_add) {
-  static_assert(!GATHER || MODE != kTN, "the gathered operand is the row-major a of a forward or dgrad product");
   static_assert(!SWIGLU || MODE != kTN, "the gated product is a forward product");
   // SWIGLU: two right operands of n columns each, b (gate) and b2 (up).  The
   // schedule runs over 2n virtual columns, 256 per tile: accumulator columns
@@ -330,7 +330,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               const int r0 = t.k_row0 + k0;
 #pragma unroll
               for (int j = 0; j < kBlockM / 64; ++j)
-                ptx::tma_load_2d(sa + j * kBoxBytes, tn_a, local_bar, t.row0 + j * 64, r0);
+                if (!GATHER) ptx::tma_load_2d(sa + j * kBoxBytes, tn_a, local_bar, t.row0 + j * 64, r0);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
                 ptx::tma_load_2d(sb + j * kBoxBytes, tn_b, local_bar, t.col0 + j * 64, r0);
@@ -359,7 +359,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               const int r0 = t.k_row0 + k0;
 #pragma unroll
               for (int j = 0; j < kBlockM / 64; ++j)
-                ptx::tma_load_2d_pair(sa + j * kBoxBytes, tn_a, bar, t.row0 + row_off + j * 64, r0);
+                if (!GATHER) ptx::tma_load_2d_pair(sa + j * kBoxBytes, tn_a, bar, t.row0 + row_off + j * 64, r0);
 #pragma unroll
               for (int j = 0; j < G::kBCols / 64; ++j)
                 ptx::tma_load_2d_pair(sb + j * kBoxBytes, tn_b, bar, t.col0 + col_off + j * 64, r0);
@@ -451,6 +451,55 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     bool bad_index = false;
     while (ok && walk.next(&t)) {
       const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+      if (MODE == kTN) {
+        // wgrad: the gathered rows are the contraction.  A k-block is 64 grouped rows
+        // (k_row0 + 64 kb ..) by this CTA's 128 columns of a_src, staged as two
+        // MN-major boxes of 64 columns: row r of box j at j * 8 KiB + 128 r, chunk
+        // index ^= r % 8.  A lane serves rows sub, sub + 4, .. sub + 60 of both boxes.
+        // Rows past the expert's last one are zeros (what the clipped tensor map
+        // does for the operand that TMA loads).
+        for (; next < base + nkb; next += kStages) {
+          const int k0 = (next - base) * kBlockK;
+          int idx[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int r = k0 + i * 4 + sub;  // row inside the expert
+            idx[i] = -1;
+            if (r < t.k_len) {
+              const int ix = a_rows[t.k_row0 + r];
+              if (ix >= 0 && ix < a_src_rows) idx[i] = ix;
+              else bad_index = true;
+            }
+          }
+          if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, abort_flag);
+          ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+          if (!ok) break;
+#pragma unroll
+          for (int j = 0; j < kBlockM / 64; ++j) {
+            const int col = t.row0 + row_off + j * 64 + chunk * 8;  // column of a_src
+            const bool in_m = col < p.d1;  // d1 is a multiple of 8
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int r = i * 4 + sub;
+              const uint32_t dst = stage_addr + uint32_t(j) * kBoxBytes + uint32_t(r) * 128u +
+                                   (uint32_t(chunk ^ (r & 7)) << 4);
+              const bool live = in_m && idx[i] >= 0;
+              ptx::cp_async_16(dst, live ? static_cast<const void*>(a_src + int64_t(idx[i]) * p.d1 + col) : a_src,
+                               live ? 16u : 0u);
+            }
+          }
+          ptx::cp_async_wait_all();
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (kPair) ptx::mbar_arrive_cluster(full_bar);
+            else ptx::mbar_arrive(full_bar);
+          }
+          ph ^= 1u;
+        }
+        base += nkb;
+        continue;
+      }
       if (next < base + nkb) {
         int idx[32];
 #pragma unroll

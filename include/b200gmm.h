@@ -198,6 +198,24 @@ int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index,
                        uint32_t* device_status, void* cuda_stream);
 
 /*
+ * The weight gradient that goes with b200gmm_run_gather: for every expert i
+ *   c[i] = x[row_index[rows_i], :]^T @ grad[rows_i, :]     ([dim_x1, n], zeros if empty)
+ * i.e. b200gmm_run with trans_a = 1 whose left operand is gathered from `x`
+ * (bf16 [x_rows, dim_x1]) through row_index (device int32 [tokens]) instead of
+ * being read from a permuted copy.  grad is bf16 [tokens, n], grouped by expert;
+ * c is bf16 [z, dim_x1, n].  Index checks as in b200gmm_run_gather.
+ * (The input gradient of the gathered product is b200gmm_run_combine with
+ * accumulate = 1 and the same row_index as destinations.)
+ * The reference has no counterpart.
+ */
+int b200gmm_run_gather_wgrad(const void* x, int64_t x_rows, const int32_t* row_index,
+                             const void* grad, void* c,
+                             const int64_t* batch_sizes, int batch_sizes_on_device,
+                             int z, int64_t tokens, int64_t dim_x1, int64_t n,
+                             void* workspace, size_t workspace_bytes,
+                             uint32_t* device_status, void* cuda_stream);
+
+/*
  * Gated forward product of a SwiGLU expert layer in one kernel:
  *   c[rows_i, :] = silu(a[rows_i, :] @ b_gate[i]) * (a[rows_i, :] @ b_up[i])
  * with silu(x) = x / (1 + exp(-x)).  b_gate and b_up have the shape b has in

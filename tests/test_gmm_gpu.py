@@ -648,6 +648,64 @@ def test_gmm_scatter_weighted_topk_combine(gg, trans_b):
     assert gg.backend.device_status() == 0
 
 
+@pytest.mark.parametrize("sizes,k,n", [
+    ([300, 0, 5, 700, 129, 64, 1, 513], 200, 328),   # ragged k-blocks, empty expert, m and n tails
+    ([64, 64, 64, 64], 128, 256),                     # whole k-blocks
+    ([1500, 0, 3000, 37, 4100, 900, 2, 1025], 1000, 1536),  # many k-blocks per tile, many tiles
+])
+def test_gmm_gather_wgrad_matches_plain_wgrad(gg, sizes, k, n):
+    """x[idx]^T @ grad per expert with the gather inside the kernel: bit-identical to
+    the plain wgrad on the permuted copy (same tiles, same arithmetic)."""
+    torch.manual_seed(19)
+    T, R = sum(sizes), 2000
+    x = torch.randn(R, k, device="cuda").bfloat16()
+    idx = torch.randint(0, R, (T,), device="cuda")
+    grad = torch.randn(T, n, device="cuda").bfloat16()
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    want = gg.backend.gmm(x[idx].contiguous(), grad, bs, trans_a=True)
+    for _ in range(2):
+        got = gg.backend.gmm_gather_wgrad(x, idx, grad, bs)
+        assert torch.equal(got, want)
+    util.assert_close(want, gmm_oracle.gmm(x[idx].cpu(), grad.cpu(), bs.cpu(), trans_a=True), atol=3e-2, rtol=2e-2,
+                      what="wgrad")
+    assert gg.backend.device_status() == 0
+
+
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_fused_gmm_gather_autograd(gg, trans_b):
+    """fused.gmm_gather(x, idx, b) against ops.gmm(x[idx], b): same value, same
+    gradients for x (summed over the rows that share a token) and b."""
+    from grouped_gemm_b200 import fused
+    torch.manual_seed(20)
+    sizes = [300, 0, 5, 700, 129, 64]
+    T, R, k, n = sum(sizes), 500, 200, 328
+    x0 = torch.randn(R, k, device="cuda").bfloat16()
+    b0 = (torch.randn(len(sizes), n, k, device="cuda") if trans_b else torch.randn(len(sizes), k, n, device="cuda")).bfloat16() * 0.1
+    idx = torch.randint(0, R, (T,), device="cuda")
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    dy = torch.randn(T, n, device="cuda").bfloat16()
+    x1, b1 = x0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    y1 = fused.gmm_gather(x1, idx, b1, bs, trans_b)
+    y1.backward(dy)
+    x2, b2 = x0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    y2 = gg.ops.gmm(x2[idx], b2, bs, trans_b)
+    y2.backward(dy)
+    assert torch.equal(y1, y2)
+    assert torch.equal(b1.grad, b2.grad)
+    # x.grad: every token's row is the sum of the bf16 dgrad rows that name it.  The
+    # fused path adds them in bf16 in memory (each addition rounds a partial sum that
+    # is at most the sum of magnitudes), so the bound grows with the number of rows.
+    rows = gg.backend.gmm(dy, b0, bs, trans_b=not trans_b).float()
+    ref = torch.zeros(R, k, device="cuda").index_add_(0, idx, rows)
+    mag = torch.zeros(R, k, device="cuda").index_add_(0, idx, rows.abs())
+    count = torch.bincount(idx, minlength=R).float()[:, None]
+    bound = 2.0 ** -8 * (count + 1) * mag + 1e-3
+    err = (x1.grad.float() - ref).abs()
+    assert bool((err <= bound).all()), f"x.grad: max excess {float((err - bound).max()):.4g}"
+    err2 = (x2.grad.float() - ref).abs()   # torch's own bf16 index backward, same bound
+    assert bool((err2 <= bound).all()), f"unfused x.grad: max excess {float((err2 - bound).max()):.4g}"
+
+
 def test_status_flags_bad_batch_sizes(gg):
     """sum(batch_sizes) > rows of a: the kernel clamps, writes nothing out of
     bounds and raises the overflow status bit."""
