@@ -152,7 +152,9 @@ def gmm_gather_wgrad(x, row_index, grad, batch_sizes, c=None):
     """``gmm(x[row_index], grad, batch_sizes, trans_a=True)`` without materialising
     ``x[row_index]``: the weight gradient of ``gmm_gather`` (no counterpart in the
     reference).  ``x`` bf16 [R, k]; ``row_index`` integer [T]; ``grad`` bf16 [T, n]
-    grouped by expert; returns bf16 [z, k, n] (zeros for empty experts)."""
+    grouped by expert; returns bf16 [z, k, n] (zeros for empty experts).  Measured
+    at 1.7x the time of ``gmm(x.index_select(0, idx), grad, trans_a=True)`` on large
+    shapes: it saves the copy, not time."""
     assert x.ndim == 2 and grad.ndim == 2 and batch_sizes.ndim == 1 and row_index.ndim == 1
     if not (x.is_cuda and grad.is_cuda and row_index.is_cuda):
         raise RuntimeError("gmm_gather_wgrad: x, grad and row_index must be CUDA tensors")

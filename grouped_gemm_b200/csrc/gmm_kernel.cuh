@@ -458,12 +458,11 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         // index ^= r % 8.  A lane serves rows sub, sub + 4, .. sub + 60 of both boxes.
         // Rows past the expert's last one are zeros (what the clipped tensor map
         // does for the operand that TMA loads).
-        for (; next < base + nkb; next += kStages) {
-          const int k0 = (next - base) * kBlockK;
-          int idx[16];
+        int idx[16];  // source rows of this lane's 16 rows of the k-block, -1 = zeros
+        auto load_idx = [&](int kb) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            const int r = k0 + i * 4 + sub;  // row inside the expert
+            const int r = kb * kBlockK + i * 4 + sub;  // row inside the expert
             idx[i] = -1;
             if (r < t.k_len) {
               const int ix = a_rows[t.k_row0 + r];
@@ -471,6 +470,9 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               else bad_index = true;
             }
           }
+        };
+        if (next < base + nkb) load_idx(next - base);
+        for (; next < base + nkb; next += kStages) {
           if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, abort_flag);
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
@@ -488,6 +490,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
                                live ? 16u : 0u);
             }
           }
+          // the indices of this warp's next k-block of the tile arrive while the copies fly
+          if (next + kStages < base + nkb) load_idx(next + kStages - base);
           ptx::cp_async_wait_all();
           ptx::fence_proxy_async_smem();
           __syncwarp();
