@@ -74,3 +74,8 @@ def test_fused_entry_points_refuse_cpu_tensors():
         backend.gmm_gather(a, torch.arange(8), b, bs)
     with pytest.raises(RuntimeError):
         backend.gmm_scatter(a, b, bs, _t(8, 24), torch.arange(8))
+    with pytest.raises(RuntimeError):
+        backend.gmm_gather_wgrad(a, torch.arange(8), _t(8, 24), bs)
+    from grouped_gemm_b200 import fused
+    with pytest.raises(RuntimeError):
+        fused.gmm_gather(a, torch.arange(8), b, bs)
