@@ -71,17 +71,31 @@ struct DeviceInfo {
   bool attrs_set = false;
 };
 
-template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
-cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, const CUtensorMap& map_b,
-                       const CUtensorMap& map_b2, const CUtensorMap& map_c, __nv_bfloat16* c, const int64_t* bs, const Problem& p, uint32_t* status,
-                       CUtensorMap* slots, const int64_t* row_dest, const int32_t* a_rows = nullptr,
-                       const __nv_bfloat16* a_src = nullptr, int64_t a_src_rows = 0,
-                       const float* row_scale = nullptr, int reduce_add = 0) {
+// Everything one launch of gmm_kernel needs, whatever the variant.
+struct LaunchArgs {
+  int grid = 0;
+  cudaStream_t stream = nullptr;
+  CUtensorMap map_a, map_b, map_b2, map_c;
+  __nv_bfloat16* c = nullptr;
+  const int64_t* batch_sizes = nullptr;  // device
+  Problem p;
+  uint32_t* status = nullptr;
+  CUtensorMap* slots = nullptr;
+  const int64_t* row_dest = nullptr;      // scatter / combine epilogue
+  const float* row_scale = nullptr;
+  int reduce_add = 0;
+  const int32_t* a_rows = nullptr;        // gather variant
+  const __nv_bfloat16* a_src = nullptr;
+  int64_t a_src_rows = 0;
+};
+
+template <int MODE, int CTAS, bool GATHER, bool SWIGLU>
+cudaError_t launch_gmm(const LaunchArgs& a) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid);
+  cfg.gridDim = dim3(a.grid);
   cfg.blockDim = dim3(GATHER ? gather_threads<CTAS, MODE>() : kThreads);
   cfg.dynamicSmemBytes = kSmemBytes;
-  cfg.stream = stream;
+  cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CTAS;
@@ -89,8 +103,23 @@ cudaError_t launch_gmm(int grid, cudaStream_t stream, const CUtensorMap& map_a, 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, map_a, map_b, map_b2, map_c, c, bs, p, status, slots,
-                            row_dest, a_rows, a_src, a_src_rows, row_scale, reduce_add);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, a.map_a, a.map_b, a.map_b2, a.map_c, a.c,
+                            a.batch_sizes, a.p, a.status, a.slots, a.row_dest, a.a_rows, a.a_src, a.a_src_rows,
+                            a.row_scale, a.reduce_add);
+}
+
+// The layout (a.p.mode) picks the last template argument; the gated product has no wgrad form.
+template <int CTAS, bool GATHER, bool SWIGLU>
+cudaError_t launch_layout(const LaunchArgs& a) {
+  if (a.p.mode == kNN) return launch_gmm<kNN, CTAS, GATHER, SWIGLU>(a);
+  if (a.p.mode == kNT) return launch_gmm<kNT, CTAS, GATHER, SWIGLU>(a);
+  if constexpr (!SWIGLU) return launch_gmm<kTN, CTAS, GATHER, false>(a);
+  return cudaErrorInvalidValue;
+}
+
+template <bool GATHER, bool SWIGLU>
+cudaError_t launch_variant(const LaunchArgs& a, int ctas) {
+  return ctas == 2 ? launch_layout<2, GATHER, SWIGLU>(a) : launch_layout<1, GATHER, SWIGLU>(a);
 }
 
 template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
@@ -403,38 +432,30 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     if ((rc = encode_map(&map_c, c, 2, dc, bc, CU_TENSOR_MAP_SWIZZLE_64B)) != 0) return rc;
   }
 
-  __nv_bfloat16* cp = static_cast<__nv_bfloat16*>(c);
-  cudaError_t err;
-  const __nv_bfloat16* ap = static_cast<const __nv_bfloat16*>(a);
+  LaunchArgs la;
   const int max_grid = (ctas == 2) ? dev->pair_ctas : dev->sm_count;
-  const int grid = max_grid < kMaxCtas ? max_grid : kMaxCtas;
+  la.grid = max_grid < kMaxCtas ? max_grid : kMaxCtas;
+  la.stream = stream;
+  la.map_a = map_a;
+  la.map_b = map_b;
+  la.map_b2 = map_b2;
+  la.map_c = map_c;
+  la.c = static_cast<__nv_bfloat16*>(c);
+  la.batch_sizes = bs_dev;
+  la.p = p;
+  la.status = device_status;
+  la.slots = slots;
+  la.row_dest = row_dest;
+  la.row_scale = row_scale;
+  la.reduce_add = reduce_add;
   if (gather) {
-    if (ctas == 2) {
-      if (p.mode == kNN) err = launch_gmm<kNN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
-      else if (p.mode == kTN) err = launch_gmm<kTN, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
-      else err = launch_gmm<kNT, 2, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
-    } else {
-      if (p.mode == kNN) err = launch_gmm<kNN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
-      else if (p.mode == kTN) err = launch_gmm<kTN, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
-      else err = launch_gmm<kNT, 1, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, a_rows, ap, a_source_rows, row_scale, reduce_add);
-    }
-  } else if (swiglu) {
-    if (ctas == 2) {
-      if (p.mode == kNN) err = launch_gmm<kNN, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-      else err = launch_gmm<kNT, 2, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-    } else {
-      if (p.mode == kNN) err = launch_gmm<kNN, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-      else err = launch_gmm<kNT, 1, false, true>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-    }
-  } else if (ctas == 2) {
-    if (p.mode == kNN) err = launch_gmm<kNN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-    else err = launch_gmm<kTN, 2>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-  } else {
-    if (p.mode == kNN) err = launch_gmm<kNN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-    else if (p.mode == kNT) err = launch_gmm<kNT, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
-    else err = launch_gmm<kTN, 1>(grid, stream, map_a, map_b, map_b2, map_c, cp, bs_dev, p, device_status, slots, row_dest, nullptr, nullptr, 0, row_scale, reduce_add);
+    la.a_rows = a_rows;
+    la.a_src = static_cast<const __nv_bfloat16*>(a);
+    la.a_src_rows = a_source_rows;
   }
+  const cudaError_t err = gather   ? launch_variant<true, false>(la, ctas)
+                          : swiglu ? launch_variant<false, true>(la, ctas)
+                                   : launch_variant<false, false>(la, ctas);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
     return B200GMM_ECUDA;
