@@ -79,3 +79,57 @@ def test_fused_entry_points_refuse_cpu_tensors():
     from grouped_gemm_b200 import fused
     with pytest.raises(RuntimeError):
         fused.gmm_gather(a, torch.arange(8), b, bs)
+
+
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_fused_gather_autograd_plumbing(monkeypatch, trans_b):
+    """The operand choice of fused.GatheredGroupedGemm.backward, checked on CPU by
+    standing the oracle in for the four kernels it calls: the gradients must equal
+    those autograd derives for gmm(x[idx], b) written as a per-expert loop."""
+    from grouped_gemm_b200 import fused
+    from oracle import gmm_oracle
+
+    def fake_gather(x, idx, b, bs, trans_b=False):
+        return gmm_oracle.gmm(x[idx], b, bs, trans_b=trans_b)
+
+    def fake_scatter(a, b, bs, out, row_index, trans_b=False, row_weight=None, accumulate=False):
+        rows = gmm_oracle.gmm(a, b, bs, trans_b=trans_b)
+        assert accumulate and row_weight is None
+        return out.index_add_(0, row_index, rows)
+
+    def fake_gather_wgrad(x, idx, grad, bs):
+        return gmm_oracle.gmm(x[idx], grad, bs, trans_a=True)
+
+    def fake_gmm(a, b, bs, trans_a=False, trans_b=False, c=None):
+        return gmm_oracle.gmm(a, b, bs, trans_a=trans_a, trans_b=trans_b)
+
+    monkeypatch.setattr(fused.backend, "gmm_gather", fake_gather)
+    monkeypatch.setattr(fused.backend, "gmm_scatter", fake_scatter)
+    monkeypatch.setattr(fused.backend, "gmm_gather_wgrad", fake_gather_wgrad)
+    monkeypatch.setattr(fused.backend, "gmm", fake_gmm)
+
+    torch.manual_seed(5)
+    sizes, R, k, n = [5, 0, 9, 2], 12, 16, 24
+    T = sum(sizes)
+    bs = torch.tensor(sizes)
+    idx = torch.randint(0, R, (T,))
+    x0 = torch.randn(R, k, dtype=torch.float64)
+    b0 = torch.randn(len(sizes), n, k, dtype=torch.float64) if trans_b else torch.randn(len(sizes), k, n, dtype=torch.float64)
+    dy = torch.randn(T, n, dtype=torch.float64)
+
+    x1, b1 = x0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    y1 = fused.gmm_gather(x1, idx, b1, bs, trans_b)
+    y1.backward(dy)
+
+    x2, b2 = x0.clone().requires_grad_(True), b0.clone().requires_grad_(True)
+    a2, out, start = x2[idx], [], 0
+    for i, size in enumerate(sizes):
+        rhs = b2[i].t() if trans_b else b2[i]
+        out.append(a2[start:start + size] @ rhs)
+        start += size
+    y2 = torch.cat(out)
+    y2.backward(dy)
+    # the oracle multiplies in fp32
+    assert torch.allclose(y1, y2.detach(), rtol=1e-4, atol=1e-4)
+    assert torch.allclose(x1.grad, x2.grad, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(b1.grad, b2.grad, rtol=1e-4, atol=1e-4)
