@@ -312,6 +312,61 @@ def time_loop(fn, iters):
     return e0.elapsed_time(e1) / iters
 
 
+def median_rounds(fn, iters, rounds):
+    """``rounds`` timed loops of ``iters`` calls each; ms per call: median, min, max."""
+    vals = sorted(time_loop(fn, iters) for _ in range(rounds))
+    return {"ms": vals[len(vals) // 2], "ms_min": vals[0], "ms_max": vals[-1], "rounds": rounds, "iters": iters}
+
+
+def library_loop_fns(a, b, grad, sizes):
+    """The reference's default GPU path on the same tensors: one library GEMM per
+    expert (what csrc/grouped_gemm.cu:396-435 of the reference does through
+    cublasGemmEx), here as ``torch.matmul`` on row slices.  Needs batch sizes on
+    the host, as the reference's cuBLAS build does."""
+    offs = [0]
+    for v in sizes:
+        offs.append(offs[-1] + v)
+    z = len(sizes)
+    c = torch.empty(a.shape[0], b.shape[2], device=a.device, dtype=a.dtype)
+    dx = torch.empty_like(a)
+    dw = torch.empty_like(b)
+
+    def fwd():
+        for i in range(z):
+            if sizes[i]:
+                torch.matmul(a[offs[i]:offs[i + 1]], b[i], out=c[offs[i]:offs[i + 1]])
+
+    def dgrad():
+        for i in range(z):
+            if sizes[i]:
+                torch.matmul(grad[offs[i]:offs[i + 1]], b[i].t(), out=dx[offs[i]:offs[i + 1]])
+
+    def wgrad():
+        for i in range(z):
+            torch.matmul(a[offs[i]:offs[i + 1]].t(), grad[offs[i]:offs[i + 1]], out=dw[i])
+
+    return {"fwd": fwd, "dgrad": dgrad, "wgrad": wgrad}
+
+
+def compare_passes(ours, loop, flops, iters, rounds):
+    """Each pass of this library and of the per-expert library loop, timed in turn
+    inside every round so that both see the same clocks; medians over the rounds."""
+    acc = {name: {"ours": [], "loop": []} for name in ours}
+    for fn in list(ours.values()) + list(loop.values()):
+        fn()
+    for _ in range(rounds):
+        for name in ours:
+            acc[name]["ours"].append(time_loop(ours[name], iters))
+            acc[name]["loop"].append(time_loop(loop[name], iters))
+    passes, lib = {}, {}
+    for name, v in acc.items():
+        o, l = sorted(v["ours"]), sorted(v["loop"])
+        om, lm = o[len(o) // 2], l[len(l) // 2]
+        passes[name] = {"ms": om, "ms_min": o[0], "ms_max": o[-1], "tflops": flops / om / 1e9}
+        lib[name] = {"ms": lm, "ms_min": l[0], "ms_max": l[-1], "tflops": flops / lm / 1e9, "ours_over_loop": lm / om}
+    return passes, lib
+
+
 def run_single(args):
     from grouped_gemm_b200 import _capi, backend
     dev = torch.device("cuda", 0)
@@ -339,40 +394,48 @@ def run_single(args):
 
     for _ in range(args.warmup):
         step()
+    # K steps per round, timed on the device; the value is the median round
     launches0 = _capi.launch_count()
+    round_ms = []
     with ClockSampler(0) as clocks:
-        ms_total = timed_region(step, args.steps, 1)
-    launches = _capi.launch_count() - launches0
-    ms_step = ms_total / args.steps
+        for _ in range(args.rounds):
+            round_ms.append(timed_region(step, args.steps, 1) / args.steps)
+    launches = (_capi.launch_count() - launches0) // args.rounds
+    ms_step = sorted(round_ms)[len(round_ms) // 2]
     value = 3 * flops_pass / ms_step / 1e9
 
-    # per-pass device times (each loop alone; the dominant kernel's figure feeds the roofline)
-    iters = max(args.steps, 5)
-    passes = {}
-    for name, fn in (("fwd", fwd), ("dgrad", dgrad), ("wgrad", wgrad)):
-        fn()
-        ms = time_loop(fn, iters)
-        passes[name] = {"ms": ms, "tflops": flops_pass / ms / 1e9}
+    # per-pass device times, each against the per-expert library loop on the same
+    # tensors (the dominant kernel's figure feeds the roofline)
+    iters = max(args.steps // 2, 5)
+    passes, library = compare_passes({"fwd": fwd, "dgrad": dgrad, "wgrad": wgrad},
+                                     library_loop_fns(a, b, grad, sizes), flops_pass, iters, args.rounds)
+    torch.cuda.empty_cache()
     peaks = measured_peaks()
     top = max(passes, key=lambda p: passes[p]["ms"])
     kernel_of = {"fwd": "gmm_kernel<NN>", "dgrad": "gmm_kernel<NT>", "wgrad": "gmm_kernel<TN>"}
+    traffic, traffic_source = measured_traffic(kernel_of[top])
     roofline = {
         "bound": "tensor", "kernel": kernel_of[top], "achieved": passes[top]["tflops"],
         "peak": peaks["burst"], "unit": "TFLOP/s", "frac": passes[top]["tflops"] / peaks["burst"],
         "peak_source": f"{peaks['source']} cuBLAS bf16 burst (kernel timed alone)",
         "step_frac_of_sustained": value / peaks["sustained"],
         "flops_per_launch": flops_pass, "ms_per_launch": passes[top]["ms"],
-        "traffic": TRAFFIC_BYTES.get(kernel_of[top]),
+        "traffic": traffic, "traffic_source": traffic_source,
         "algorithmic_bytes": 2.0 * (rows * k + z * k * n + rows * n),
     }
+    gpu_library_loop = {"what": "per-expert torch.matmul (cuBLAS) loop on the same tensors, batch sizes on the host; "
+                                "timed in turn with this library's pass inside each round",
+                        "mixtral_up": library}
 
     # benchmark configuration 3 also names the down-projection, b [8, 14336, 4096]
-    down = down_projection(backend, dev, bs, iters)
+    down, library_down = down_projection(backend, dev, bs, sizes, iters, args.rounds)
+    gpu_library_loop["mixtral_down"] = library_down
 
     # small-M, HBM-bound group shapes (benchmark configuration 4): report GB/s
     del a, b, grad
     torch.cuda.empty_cache()
-    hbm = fine_grained_hbm(backend, dev, peaks)
+    hbm, library_fine = fine_grained_hbm(backend, dev, peaks, args.rounds)
+    gpu_library_loop["fine_grained"] = library_fine
 
     # end to end: pinned host buffers in and out, copies inside the timed region
     g = torch.Generator(device=dev).manual_seed(1)
@@ -392,7 +455,9 @@ def run_single(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(1),
+        "rounds": {"count": args.rounds, "ms_per_step_min": min(round_ms), "ms_per_step_max": max(round_ms)},
         "passes": passes, "down_projection": down, "roofline": roofline, "hbm_bound_case": hbm,
+        "gpu_library_loop": gpu_library_loop,
         "cpu_baseline": baseline,
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks.summary(),
         "frac_of_nominal_2250": value / 2250.0, "device_status": backend.device_status(),
@@ -404,14 +469,61 @@ def run_single(args):
     print(json.dumps(line), flush=True)
 
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) per launch at the
-# benchmark's size, from the ncu captures summarised in
-# profiles/gmm_kernel_mixtral_ncu_full.md (full-size launches, so no scaling).
-TRAFFIC_BYTES = {
-    "gmm_kernel<NN>": 4.133e9 + 0.932e9,
-    "gmm_kernel<NT>": 8.610e9 + 0.267e9,
-    "gmm_kernel<TN>": 6.367e9 + 0.918e9,
-}
+TRAFFIC_FILE = os.path.join(ROOT, "bench_traffic.json")
+
+
+def measured_traffic(kernel):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the
+    named kernel at the benchmark's size, from the file ``--traffic-from`` wrote out
+    of an ncu capture of ``--profile`` runs of this build; (None, reason) without it."""
+    if not os.path.exists(TRAFFIC_FILE):
+        return None, "no ncu capture recorded for this build (bench.py --traffic-from)"
+    with open(TRAFFIC_FILE) as f:
+        rec = json.load(f)
+    entry = rec.get("kernels", {}).get(kernel)
+    if entry is None:
+        return None, f"{os.path.basename(TRAFFIC_FILE)} has no entry for {kernel}"
+    return entry["dram_bytes"], rec.get("source", "ncu")
+
+
+def record_traffic(paths):
+    """--traffic-from CSV [CSV ...]: read ncu --csv logs (metrics dram__bytes_read.sum,
+    dram__bytes_write.sum) of ``--profile`` runs and write the bytes per launch of
+    each gmm_kernel layout, last captured launch of each, to bench_traffic.json."""
+    import csv
+    layouts = {"0": "gmm_kernel<NN>", "1": "gmm_kernel<NT>", "2": "gmm_kernel<TN>"}
+    found = {}
+    for path in paths:
+        header = None
+        per_id = {}
+        with open(path, newline="") as f:
+            for row in csv.reader(f):
+                if row and row[0] == "ID":
+                    header = row
+                    continue
+                if header is None or len(row) != len(header):
+                    continue
+                d = dict(zip(header, row))
+                name = d["Kernel Name"]
+                if "gmm_kernel<" not in name:
+                    continue
+                mode = name.split("gmm_kernel<")[1].split(",")[0].strip().replace("(b200gmm::Mode)", "")
+                if d["Metric Name"] in ("dram__bytes_read.sum", "dram__bytes_write.sum"):
+                    value = float(d["Metric Value"].replace(",", ""))
+                    unit = d["Metric Unit"].lower()
+                    scale = {"byte": 1.0, "kbyte": 1e3, "mbyte": 1e6, "gbyte": 1e9}.get(unit, 1.0)
+                    rec = per_id.setdefault(d["ID"], {"mode": mode, "bytes": 0.0})
+                    rec["bytes"] += value * scale
+        for _, rec in sorted(per_id.items(), key=lambda kv: int(kv[0])):
+            if rec["mode"] in layouts:
+                found[layouts[rec["mode"]]] = {"dram_bytes": rec["bytes"], "capture": os.path.basename(path)}
+    out = {"source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch at the benchmark's size "
+                     "(bench.py --profile PASS under ncu, then bench.py --traffic-from)",
+           "kernels": found}
+    with open(TRAFFIC_FILE, "w") as f:
+        json.dump(out, f, indent=1)
+        f.write("\n")
+    print(json.dumps(out))
 
 
 def fused_neighbours(backend, dev, bs, rounds=6):
@@ -481,25 +593,25 @@ def fused_neighbours(backend, dev, bs, rounds=6):
     return out
 
 
-def down_projection(backend, dev, bs, iters):
-    """The three passes on the down-projection shapes (k=14336, n=4096)."""
+def down_projection(backend, dev, bs, sizes, iters, rounds):
+    """The three passes on the down-projection shapes (k=14336, n=4096), each
+    against the per-expert library loop."""
     z, rows, k, n = MIXTRAL["z"], MIXTRAL["rows"], MIXTRAL["n"], MIXTRAL["k"]
     g = torch.Generator(device=dev).manual_seed(4)
     a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
     b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
     grad = torch.randn(rows, n, device=dev, generator=g).bfloat16()
     flops = 2.0 * rows * k * n
+    ours = {"fwd": lambda: backend.gmm(a, b, bs),
+            "dgrad": lambda: backend.gmm(grad, b, bs, trans_b=True),
+            "wgrad": lambda: backend.gmm(a, grad, bs, trans_a=True)}
+    passes, library = compare_passes(ours, library_loop_fns(a, b, grad, sizes), flops, iters, rounds)
     out = {"workload": "b [8, 14336, 4096], a [32768, 14336], same batch sizes"}
-    for name, fn in (("fwd", lambda: backend.gmm(a, b, bs)),
-                     ("dgrad", lambda: backend.gmm(grad, b, bs, trans_b=True)),
-                     ("wgrad", lambda: backend.gmm(a, grad, bs, trans_a=True))):
-        fn()
-        ms = time_loop(fn, iters)
-        out[name] = {"ms": ms, "tflops": flops / ms / 1e9}
-    return out
+    out.update(passes)
+    return out, library
 
 
-def fine_grained_hbm(backend, dev, peaks):
+def fine_grained_hbm(backend, dev, peaks, rounds):
     """benchmark configuration 4 (z=256, k=7168, n=2048, 65536 rows, ~20 % empty experts;
     median group 59 rows): the weights (forward, dgrad) or the per-expert outputs
     (wgrad) dominate the traffic, so these passes are judged against the HBM
@@ -517,16 +629,20 @@ def fine_grained_hbm(backend, dev, peaks):
     nbytes = {"fwd": 2.0 * (rows * k + nonempty * k * n + rows * n),
               "dgrad": 2.0 * (rows * n + nonempty * k * n + rows * k),
               "wgrad": 2.0 * (rows * k + rows * n + z * k * n)}
+    c_w = torch.empty(z, k, n, device=dev, dtype=torch.bfloat16)
+    ours = {"fwd": lambda: backend.gmm(a, b, bs),
+            "dgrad": lambda: backend.gmm(grad, b, bs, trans_b=True),
+            "wgrad": lambda: backend.gmm(a, grad, bs, trans_a=True, c=c_w)}
+    passes, library = compare_passes(ours, library_loop_fns(a, b, grad, sizes), flops, 5, rounds)
     out = {"workload": "config 4: z=256 k=7168 n=2048 rows=65536, 51 empty experts, median 59 rows"}
-    for name, fn in (("fwd", lambda: backend.gmm(a, b, bs)),
-                     ("dgrad", lambda: backend.gmm(grad, b, bs, trans_b=True)),
-                     ("wgrad", lambda: backend.gmm(a, grad, bs, trans_a=True))):
-        for _ in range(3):
-            fn()
-        ms = time_loop(fn, 10)
-        out[name] = {"ms": ms, "gbs": nbytes[name] / ms / 1e6, "hbm_frac": nbytes[name] / ms / 1e6 / peaks["hbm_gbs"],
-                     "tflops": flops / ms / 1e9, "algorithmic_bytes": nbytes[name]}
-    return out
+    for name, rec in passes.items():
+        tensor_ms = flops / peaks["burst"] / 1e9
+        hbm_ms = nbytes[name] / peaks["hbm_gbs"] / 1e6
+        rec.update({"gbs": nbytes[name] / rec["ms"] / 1e6, "hbm_frac": nbytes[name] / rec["ms"] / 1e6 / peaks["hbm_gbs"],
+                    "algorithmic_bytes": nbytes[name],
+                    "roofline_ms": max(tensor_ms, hbm_ms), "roofline_frac": max(tensor_ms, hbm_ms) / rec["ms"]})
+        out[name] = rec
+    return out, library
 
 
 def e2e_single(backend, a, b, grad, bs, flops_pass, steps):
@@ -823,6 +939,10 @@ def main():
     ap.add_argument("--profile-workload", choices=["mixtral", "fine"], default="mixtral")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--rounds", type=int, default=5,
+                    help="timed rounds of --steps steps each; the value is the median round")
+    ap.add_argument("--traffic-from", nargs="+", default=None, metavar="NCU_CSV",
+                    help="record DRAM bytes per launch from ncu --csv logs of --profile runs and exit")
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -841,6 +961,9 @@ def main():
                     help="also time the multi-GPU workload on this one GPU (strong-scaling denominator)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.traffic_from:
+        return record_traffic(args.traffic_from)
+    args.rounds = max(args.rounds, 1)
     if args.impl == "reference":
         return run_reference(args)
     world, _, _ = dist_info()

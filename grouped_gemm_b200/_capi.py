@@ -11,17 +11,19 @@ import os
 import torch  # noqa: F401
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# B200GMM_LIBRARY points at another build of the same library (A/B comparisons).
+# B200GMM_LIBRARY: path of the built library, for installs that keep it elsewhere.
 LIB_PATH = os.environ.get("B200GMM_LIBRARY") or os.path.join(_HERE, "csrc", "libb200gmm.so")
 
 OK = 0
 MAX_EXPERTS = 1024
 FILL_FIELDS = 9
+SCHEDULE_FIELDS = 6
 STATIC_MAX_EXPERTS = 256
 STATUS_TIMEOUT = 0x1
 STATUS_NEGATIVE_SIZE = 0x2
 STATUS_ROWS_OVERFLOW = 0x4
 STATUS_BAD_ROW_INDEX = 0x8
+STATUS_BAD_ROW_DEST = 0x10
 
 # name -> (restype, argtypes); exactly the symbols include/b200gmm.h declares.
 _c = ctypes
@@ -36,15 +38,16 @@ SIGNATURES = {
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_void_p]),
     "b200gmm_run_scatter": (_c.c_int, [
-        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int,
+        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_int,
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_run_combine": (_c.c_int, [
-        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_void_p,
+        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_run_gather": (_c.c_int, [
-        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64,
+        _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_run_gather_wgrad": (_c.c_int, [
@@ -52,7 +55,7 @@ SIGNATURES = {
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_run_swiglu": (_c.c_int, [
-        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_push_rows": (_c.c_int, [
@@ -64,6 +67,10 @@ SIGNATURES = {
     "b200gmm_schedule_host": (_c.c_int, [
         _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_int64, _c.POINTER(_c.c_int64)]),
+    "b200gmm_schedule_device": (_c.c_int, [
+        _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int,
+        _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p]),
+    "b200gmm_selftest_wait_timeout": (_c.c_int, [_c.c_int64, _c.c_void_p, _c.c_void_p]),
     "b200gmm_tile_shape": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_int)]),
     "b200gmm_launch_count": (_c.c_int64, []),
     "b200gmm_strerror": (_c.c_char_p, [_c.c_int]),

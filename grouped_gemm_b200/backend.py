@@ -39,6 +39,16 @@ def gmm(a, b, batch_sizes, trans_a=False, trans_b=False, c=None):
     return out
 
 
+def _host_or_device_sizes(batch_sizes):
+    """batch_sizes as the C ABI wants it: on the device as it is; on the host
+    contiguous and pageable (the library's asynchronous copy reads a pinned array
+    only when the stream gets there, by which time the caller may have changed it)."""
+    if batch_sizes.is_cuda:
+        return batch_sizes
+    bs = batch_sizes.contiguous()
+    return bs.clone() if bs.is_pinned() else bs
+
+
 def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False, row_weight=None, accumulate=False):
     """``gmm`` with the un-sort fused into the kernel: row ``i`` of the grouped
     result is written to ``out[row_index[i]]`` instead of ``c[i]`` (no
@@ -47,7 +57,9 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False, row_weight=Non
     ``a`` [T, k] holds the rows sorted by expert as for ``gmm``; ``out`` is a
     contiguous bf16 [R, n] tensor on the same device, ``row_index`` int64 [T] with
     values in [0, R).  Rows of ``out`` that no index names are left alone; if two
-    indices coincide the later write wins in no defined order.  Returns ``out``.
+    indices coincide the later write wins in no defined order.  An index outside
+    [0, R) is never written through: the row is dropped and status bit
+    STATUS_BAD_ROW_DEST is raised.  Returns ``out``.
 
     ``row_weight`` (float32 [T], optional) multiplies row ``i`` in fp32 before the
     rounding to bf16; ``accumulate=True`` adds the rows to ``out`` instead of
@@ -60,6 +72,8 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False, row_weight=Non
     k = b.shape[2] if trans_b else b.shape[1]
     if not (a.is_cuda and b.is_cuda and out.is_cuda and row_index.is_cuda):
         raise RuntimeError("gmm_scatter: a, b, out and row_index must be CUDA tensors")
+    if not (b.device == out.device == row_index.device == a.device) or (batch_sizes.is_cuda and batch_sizes.device != a.device):
+        raise RuntimeError("gmm_scatter: a, b, out, row_index (and a CUDA batch_sizes) must be on one device")
     if not (a.dtype == b.dtype == out.dtype == torch.bfloat16) or row_index.dtype != torch.int64:
         raise RuntimeError("gmm_scatter: a, b, out must be bfloat16 and row_index int64")
     if a.shape[1] != k or out.shape[1] != n or row_index.shape[0] != a.shape[0] or batch_sizes.shape[0] != b.shape[0]:
@@ -69,24 +83,26 @@ def gmm_scatter(a, b, batch_sizes, out, row_index, trans_b=False, row_weight=Non
     if batch_sizes.dtype != torch.int64:
         raise RuntimeError("gmm_scatter: batch_sizes must be int64")
     if row_weight is not None and not (row_weight.is_cuda and row_weight.dtype == torch.float32
-                                       and row_weight.shape == (a.shape[0],) and row_weight.is_contiguous()):
-        raise RuntimeError("gmm_scatter: row_weight must be a contiguous float32 CUDA tensor [T]")
+                                       and row_weight.shape == (a.shape[0],) and row_weight.is_contiguous()
+                                       and row_weight.device == a.device):
+        raise RuntimeError("gmm_scatter: row_weight must be a contiguous float32 CUDA tensor [T] on a's device")
     lib = _capi.load()
     z = batch_sizes.shape[0]
     with torch.cuda.device(a.device):
         dest = row_index * (n * 2) + out.data_ptr()          # byte address of every destination row
+        window = (out.data_ptr(), out.numel() * 2)           # the kernel refuses addresses outside ``out``
         ws_bytes = _capi.workspace_bytes(z)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
-        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        bs = _host_or_device_sizes(batch_sizes)
         status = backend.device_status(a.device).data_ptr()
         stream = torch.cuda.current_stream(a.device).cuda_stream
         if row_weight is None and not accumulate:
             rc = lib.b200gmm_run_scatter(
-                a.data_ptr(), b.data_ptr(), dest.data_ptr(), bs.data_ptr(), 1 if bs.is_cuda else 0, z,
+                a.data_ptr(), b.data_ptr(), dest.data_ptr(), *window, bs.data_ptr(), 1 if bs.is_cuda else 0, z,
                 a.shape[0], a.shape[1], n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes, status, stream)
         else:
             rc = lib.b200gmm_run_combine(
-                a.data_ptr(), b.data_ptr(), dest.data_ptr(),
+                a.data_ptr(), b.data_ptr(), dest.data_ptr(), *window,
                 None if row_weight is None else row_weight.data_ptr(), 1 if accumulate else 0,
                 bs.data_ptr(), 1 if bs.is_cuda else 0, z,
                 a.shape[0], a.shape[1], n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes, status, stream)
@@ -113,6 +129,8 @@ def gmm_gather(x, row_index, b, batch_sizes, trans_b=False, c=None, out=None, ou
     k = b.shape[2] if trans_b else b.shape[1]
     if not (x.is_cuda and b.is_cuda and row_index.is_cuda):
         raise RuntimeError("gmm_gather: x, b and row_index must be CUDA tensors")
+    if not (b.device == row_index.device == x.device) or (batch_sizes.is_cuda and batch_sizes.device != x.device):
+        raise RuntimeError("gmm_gather: x, b, row_index (and a CUDA batch_sizes) must be on one device")
     if not (x.dtype == b.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
         raise RuntimeError("gmm_gather: x and b must be bfloat16, batch_sizes int64")
     if x.shape[1] != k or batch_sizes.shape[0] != b.shape[0] or not (x.is_contiguous() and b.is_contiguous()):
@@ -123,25 +141,27 @@ def gmm_gather(x, row_index, b, batch_sizes, trans_b=False, c=None, out=None, ou
     z = batch_sizes.shape[0]
     with torch.cuda.device(x.device):
         dest_ptr = None
+        window = (None, 0)
         result = None
         if out is not None:
             if out_index is None or out.dtype != torch.bfloat16 or not out.is_contiguous() or out.shape[1] != n \
-                    or out_index.shape[0] != tokens:
-                raise RuntimeError("gmm_gather: out must be contiguous bf16 [R2, n] with out_index int64 [T]")
+                    or out_index.shape[0] != tokens or out.device != x.device or out_index.device != x.device:
+                raise RuntimeError("gmm_gather: out must be contiguous bf16 [R2, n] with out_index int64 [T], on x's device")
             dest = out_index.to(torch.int64) * (n * 2) + out.data_ptr()
             dest_ptr, result = dest.data_ptr(), out
+            window = (out.data_ptr(), out.numel() * 2)
             c_ptr = None
         else:
             if c is None:
                 c = torch.empty(tokens, n, device=x.device, dtype=x.dtype)
-            elif c.shape != (tokens, n) or c.dtype != torch.bfloat16 or not c.is_contiguous():
-                raise RuntimeError("gmm_gather: c must be contiguous bf16 [len(row_index), n]")
+            elif c.shape != (tokens, n) or c.dtype != torch.bfloat16 or not c.is_contiguous() or c.device != x.device:
+                raise RuntimeError("gmm_gather: c must be contiguous bf16 [len(row_index), n] on x's device")
             c_ptr, result = c.data_ptr(), c
         ws_bytes = _capi.workspace_bytes(z)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
-        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        bs = _host_or_device_sizes(batch_sizes)
         rc = lib.b200gmm_run_gather(
-            x.data_ptr(), x.shape[0], idx32.data_ptr(), b.data_ptr(), c_ptr, dest_ptr, bs.data_ptr(),
+            x.data_ptr(), x.shape[0], idx32.data_ptr(), b.data_ptr(), c_ptr, dest_ptr, *window, bs.data_ptr(),
             1 if bs.is_cuda else 0, z, tokens, k, n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
             backend.device_status(x.device).data_ptr(), torch.cuda.current_stream(x.device).cuda_stream)
     _capi.check(rc, "b200gmm_run_gather")
@@ -158,6 +178,8 @@ def gmm_gather_wgrad(x, row_index, grad, batch_sizes, c=None):
     assert x.ndim == 2 and grad.ndim == 2 and batch_sizes.ndim == 1 and row_index.ndim == 1
     if not (x.is_cuda and grad.is_cuda and row_index.is_cuda):
         raise RuntimeError("gmm_gather_wgrad: x, grad and row_index must be CUDA tensors")
+    if not (grad.device == row_index.device == x.device) or (batch_sizes.is_cuda and batch_sizes.device != x.device):
+        raise RuntimeError("gmm_gather_wgrad: x, grad, row_index (and a CUDA batch_sizes) must be on one device")
     if not (x.dtype == grad.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
         raise RuntimeError("gmm_gather_wgrad: x and grad must be bfloat16, batch_sizes int64")
     tokens, n, k, z = grad.shape[0], grad.shape[1], x.shape[1], batch_sizes.shape[0]
@@ -172,7 +194,7 @@ def gmm_gather_wgrad(x, row_index, grad, batch_sizes, c=None):
     with torch.cuda.device(x.device):
         ws_bytes = _capi.workspace_bytes(z)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device)
-        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        bs = _host_or_device_sizes(batch_sizes)
         rc = lib.b200gmm_run_gather_wgrad(
             x.data_ptr(), x.shape[0], idx32.data_ptr(), grad.data_ptr(), c.data_ptr(), bs.data_ptr(),
             1 if bs.is_cuda else 0, z, tokens, k, n, ws.data_ptr(), ws_bytes,
@@ -196,6 +218,8 @@ def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False, c=None):
     k = b_gate.shape[2] if trans_b else b_gate.shape[1]
     if not (a.is_cuda and b_gate.is_cuda and b_up.is_cuda):
         raise RuntimeError("gmm_swiglu: a, b_gate and b_up must be CUDA tensors")
+    if not (b_gate.device == b_up.device == a.device) or (batch_sizes.is_cuda and batch_sizes.device != a.device):
+        raise RuntimeError("gmm_swiglu: a, b_gate, b_up (and a CUDA batch_sizes) must be on one device")
     if not (a.dtype == b_gate.dtype == b_up.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
         raise RuntimeError("gmm_swiglu: a, b_gate, b_up must be bfloat16, batch_sizes int64")
     if b_gate.shape != b_up.shape or a.shape[1] != k or batch_sizes.shape[0] != b_gate.shape[0]:
@@ -212,9 +236,9 @@ def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False, c=None):
     with torch.cuda.device(a.device):
         ws_bytes = _capi.workspace_bytes(z)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
-        bs = batch_sizes if batch_sizes.is_cuda else batch_sizes.contiguous()
+        bs = _host_or_device_sizes(batch_sizes)
         rc = lib.b200gmm_run_swiglu(
-            a.data_ptr(), b_gate.data_ptr(), b_up.data_ptr(), c.data_ptr(), None, bs.data_ptr(),
+            a.data_ptr(), b_gate.data_ptr(), b_up.data_ptr(), c.data_ptr(), None, None, 0, bs.data_ptr(),
             1 if bs.is_cuda else 0, z, tokens, k, n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
             backend.device_status(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
     _capi.check(rc, "b200gmm_run_swiglu")

@@ -9,7 +9,9 @@
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <mutex>
+#include <vector>
 
 #include "ep_exchange.cuh"
 #include "gmm_kernel.cuh"
@@ -75,18 +77,20 @@ struct DeviceInfo {
 struct LaunchArgs {
   int grid = 0;
   cudaStream_t stream = nullptr;
-  CUtensorMap map_a, map_b, map_b2, map_c;
+  CUtensorMap map_a, map_b, map_b2, map_c, map_a2;
   __nv_bfloat16* c = nullptr;
   const int64_t* batch_sizes = nullptr;  // device
   Problem p;
   uint32_t* status = nullptr;
   CUtensorMap* slots = nullptr;
+  uint32_t* sched_counter = nullptr;       // zeroed on the stream before the launch
   const int64_t* row_dest = nullptr;      // scatter / combine epilogue
   const float* row_scale = nullptr;
   int reduce_add = 0;
   const int32_t* a_rows = nullptr;        // gather variant
   const __nv_bfloat16* a_src = nullptr;
   int64_t a_src_rows = 0;
+  int64_t dest_lo = 0, dest_hi = 0;       // window every row_dest entry must fall into (0, 0: unchecked)
 };
 
 template <int MODE, int CTAS, bool GATHER, bool SWIGLU>
@@ -103,9 +107,9 @@ cudaError_t launch_gmm(const LaunchArgs& a) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, a.map_a, a.map_b, a.map_b2, a.map_c, a.c,
-                            a.batch_sizes, a.p, a.status, a.slots, a.row_dest, a.a_rows, a.a_src, a.a_src_rows,
-                            a.row_scale, a.reduce_add);
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, a.map_a, a.map_b, a.map_b2, a.map_c, a.map_a2, a.c,
+                            a.batch_sizes, a.p, a.status, a.slots, a.sched_counter, a.row_dest, a.a_rows, a.a_src, a.a_src_rows,
+                            a.row_scale, a.reduce_add, a.dest_lo, a.dest_hi);
 }
 
 // The layout (a.p.mode) picks the last template argument; the gated product has no wgrad form.
@@ -190,6 +194,11 @@ int env_int(const char* name, int fallback) {
   return (v != nullptr && *v != '\0') ? std::atoi(v) : fallback;
 }
 
+int64_t env_int64(const char* name, int64_t fallback) {
+  const char* v = std::getenv(name);
+  return (v != nullptr && *v != '\0') ? std::atoll(v) : fallback;
+}
+
 // bf16 tensor map (128-byte swizzle unless told otherwise); dims/box innermost first.
 int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
                const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
@@ -228,8 +237,14 @@ int choose_ctas(int z, int64_t tokens, int64_t d1, int trans_a) {
   return (z > 0 && tokens / z >= 512) ? 2 : 1;
 }
 
+// Which kernel features a plain, gathered or gated launch uses (schedule.cuh: Problem).
+struct Features {
+  bool gather = false;
+  bool swiglu = false;
+};
+
 int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int trans_b, int ctas,
-                  Problem* p) {
+                  Problem* p, const Features& f = Features()) {
   if (trans_a && trans_b) return B200GMM_EINVAL;
   if (z < 0 || tokens < 0 || d1 < 0 || n < 0) return B200GMM_EINVAL;
   if (z > kMaxExperts) return B200GMM_ELIMIT;
@@ -246,12 +261,21 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   p->tile_m = kBlockM * ctas;
   p->group_m = env_int("B200GMM_GROUP_M", ctas == 2 ? 8 : 16);
   if (p->group_m < 1) p->group_m = 1;
-  p->direct_store = env_int("B200GMM_DIRECT_STORE", 0) != 0;
-  // Upper bound on the tile count must fit the kernel's 32-bit tile index.
+  // Tiles are drawn from a global counter.  Where tile durations differ widely
+  // (wgrad: the contraction is the expert's row count; one-CTA kernels: fine-grained
+  // experts, some a few rows, some thousands) the experts are also sorted by size and
+  // taken from both ends at once.
+  p->dynamic = env_int("B200GMM_DYNAMIC", 1) != 0;
+  p->order = (p->dynamic && z > 1 && (p->mode == kTN || ctas == 1)) ? env_int("B200GMM_ORDER", 1) : 0;
+  p->light = (p->mode != kTN && ctas == 1 && !f.gather && !f.swiglu) ? env_int("B200GMM_LIGHT", 1) : 0;
+  const int64_t wait_ns = env_int64("B200GMM_WAIT_LIMIT_NS", static_cast<int64_t>(ptx::kWaitLimitNs));
+  p->wait_ns = wait_ns > 0 ? wait_ns : static_cast<int64_t>(ptx::kWaitLimitNs);
+  // Upper bound on the tile count must fit the kernel's 32-bit tile index (twice:
+  // positions drawn past the end still have to fit).
   const int64_t nt = (n + kBlockN - 1) / kBlockN;
   const int64_t row_tiles = trans_a ? int64_t(z) * ((d1 + p->tile_m - 1) / p->tile_m)
-                                    : (tokens / p->tile_m + z);
-  if (row_tiles * nt >= (int64_t(1) << 31)) return B200GMM_ELIMIT;
+                                    : (tokens / p->tile_m + 3 * int64_t(z));  // + transposed tiles, half as wide
+  if (row_tiles * nt >= (int64_t(1) << 30)) return B200GMM_ELIMIT;
   return B200GMM_OK;
 }
 
@@ -270,20 +294,24 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 // symbol's name is only a handle; the address a kernel can use has to be asked
 // for, per device, with that device current.
 int static_scratch_address(void** out) {
+  // One lookup per device; afterwards a plain atomic load, no lock.
+  static std::atomic<void*> addr[64];
   static std::mutex mu;
-  static void* addr[64] = {nullptr};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200GMM_ECUDA;
-  std::lock_guard<std::mutex> lock(mu);
-  if (addr[dev] == nullptr) {
-    void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
-      (void)cudaGetLastError();
-      return B200GMM_ECUDA;
+  void* p = addr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
+    std::lock_guard<std::mutex> lock(mu);
+    p = addr[dev].load(std::memory_order_relaxed);
+    if (p == nullptr) {
+      if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) {
+        (void)cudaGetLastError();
+        return B200GMM_ECUDA;
+      }
+      addr[dev].store(p, std::memory_order_release);
     }
-    addr[dev] = p;
   }
-  *out = addr[dev];
+  *out = p;
   return B200GMM_OK;
 }
 
@@ -315,7 +343,9 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              int trans_a, int trans_b, void* workspace, size_t workspace_bytes,
              uint32_t* device_status, void* cuda_stream, const int64_t* row_dest,
              const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr,
-             const float* row_scale = nullptr, int reduce_add = 0) {
+             const float* row_scale = nullptr, int reduce_add = 0, const void* dest_base = nullptr,
+             int64_t dest_bytes = 0) {
+  if (dest_base != nullptr && (row_dest == nullptr || dest_bytes < 0)) return B200GMM_EINVAL;
   if ((row_scale != nullptr || reduce_add) && row_dest == nullptr) return B200GMM_EINVAL;
   if (a_rows != nullptr && (dim_a1 == 0 || a_source_rows <= 0 || (trans_a && row_dest != nullptr)))
     return B200GMM_EINVAL;
@@ -332,8 +362,11 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     if (c == nullptr) c = const_cast<void*>(a);  // never written; keeps the argument checks below uniform
   }
   Problem p;
+  Features feat;
+  feat.gather = (a_rows != nullptr);
+  feat.swiglu = swiglu;
   int ctas = choose_ctas(z, tokens, dim_a1, trans_a);
-  int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p);
+  int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p, feat);
   if (rc != B200GMM_OK) return rc;
   cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
   if (z == 0) return B200GMM_OK;
@@ -370,7 +403,7 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
 
   if (ctas == 2 && dev->pair_ctas < 2) {
     ctas = 1;
-    if ((rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p)) != B200GMM_OK) return rc;
+    if ((rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, ctas, &p, feat)) != B200GMM_OK) return rc;
   }
 
   size_t need = 0;
@@ -378,6 +411,10 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 127))
     return B200GMM_EWORKSPACE;
   CUtensorMap* slots = reinterpret_cast<CUtensorMap*>(static_cast<char*>(workspace) + maps_offset(z));
+  // The tile counter of the kernel's scheduler sits in the 16 bytes after the
+  // batch_sizes copy and starts every launch at zero.
+  uint32_t* sched_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + size_t(z) * sizeof(int64_t));
+  if (p.dynamic && cudaMemsetAsync(sched_counter, 0, 16, stream) != cudaSuccess) return B200GMM_ECUDA;
 
   const int64_t* bs_dev = batch_sizes;
   if (!batch_sizes_on_device) {
@@ -387,7 +424,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     bs_dev = static_cast<const int64_t*>(workspace);
   }
 
-  CUtensorMap map_a, map_b, map_b2;
+  CUtensorMap map_a, map_b, map_b2, map_a2;
+  bool have_b2 = swiglu;
   // N: columns of b (and of b2, and of c); the Problem's n is twice that for the gated product.
   const uint64_t T = uint64_t(tokens), D1 = uint64_t(dim_a1), N = uint64_t(n_out), Z = uint64_t(z);
   const bool gather = (a_rows != nullptr);  // a is then fetched row by row, without a tensor map
@@ -400,6 +438,10 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     if (swiglu && (rc = encode_map(&map_b2, b2, 3, db, bb)) != 0) return rc;
     if (gather) map_a = map_b;
     else if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0) return rc;
+    if (p.light) {  // transposed tiles fetch their few rows of a in boxes of 32
+      const uint32_t bl[2] = {kBlockK, 32};
+      if ((rc = encode_map(&map_a2, a, 2, da, bl)) != 0) return rc;
+    }
   } else if (p.mode == kNT) {
     const uint64_t da[2] = {D1, T};
     const uint32_t ba[2] = {kBlockK, uint32_t(kBlockM)};
@@ -410,6 +452,13 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     if (swiglu && (rc = encode_map(&map_b2, b2, 3, db, bb)) != 0) return rc;
     if (gather) map_a = map_b;
     else if ((rc = encode_map(&map_a, a, 2, da, ba)) != 0) return rc;
+    if (p.light) {  // transposed tiles: rows of a in boxes of 32, 128 rows of b[i] as the M operand
+      const uint32_t bl[2] = {kBlockK, 32};
+      const uint32_t bw[3] = {kBlockK, uint32_t(kLightCols), 1};
+      if ((rc = encode_map(&map_a2, a, 2, da, bl)) != 0) return rc;
+      if ((rc = encode_map(&map_b2, b, 3, db, bw)) != 0) return rc;
+      have_b2 = true;
+    }
   } else {
     const uint64_t da[2] = {D1, T};
     const uint64_t db[2] = {N, T};
@@ -419,7 +468,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     else if ((rc = encode_map(&map_a, a, 2, da, bx)) != 0) return rc;
   }
 
-  if (!swiglu) map_b2 = map_b;  // unused by the kernel, but a valid map
+  if (!have_b2) map_b2 = map_b;  // unused by the kernel, but a valid map
+  if (!p.light) map_a2 = map_a;
 
   // Output map for the epilogue's TMA stores: 32 x 32 boxes, 64-byte swizzle.
   // wgrad's c[z, m, n] is addressed as z*m rows.  Unused (left zeroed) when the
@@ -440,6 +490,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   la.map_b = map_b;
   la.map_b2 = map_b2;
   la.map_c = map_c;
+  la.map_a2 = map_a2;
+  la.sched_counter = sched_counter;
   la.c = static_cast<__nv_bfloat16*>(c);
   la.batch_sizes = bs_dev;
   la.p = p;
@@ -448,6 +500,11 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   la.row_dest = row_dest;
   la.row_scale = row_scale;
   la.reduce_add = reduce_add;
+  if (dest_base != nullptr) {
+    la.dest_lo = static_cast<int64_t>(reinterpret_cast<uintptr_t>(dest_base));
+    la.dest_hi = la.dest_lo + dest_bytes;
+    if (la.dest_hi == 0) la.dest_hi = 1;  // an empty window at address 0 still rejects every row
+  }
   if (gather) {
     la.a_rows = a_rows;
     la.a_src = static_cast<const __nv_bfloat16*>(a);
@@ -476,16 +533,19 @@ int b200gmm_run(const void* a, const void* b, void* c, const int64_t* batch_size
                   workspace, workspace_bytes, device_status, cuda_stream, nullptr);
 }
 
-int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest, const int64_t* batch_sizes,
+int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest, const void* dest_base,
+                        int64_t dest_bytes, const int64_t* batch_sizes,
                         int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
                         int trans_b, void* workspace, size_t workspace_bytes, uint32_t* device_status,
                         void* cuda_stream) {
   if (row_dest == nullptr) return B200GMM_EINVAL;
   return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
-                  workspace, workspace_bytes, device_status, cuda_stream, row_dest);
+                  workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr, nullptr, 0,
+                  dest_base, dest_bytes);
 }
 
-int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest, const float* row_weight,
+int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest, const void* dest_base,
+                        int64_t dest_bytes, const float* row_weight,
                         int accumulate, const int64_t* batch_sizes, int batch_sizes_on_device, int z,
                         int64_t tokens, int64_t dim_a1, int64_t n, int trans_b, void* workspace,
                         size_t workspace_bytes, uint32_t* device_status, void* cuda_stream) {
@@ -496,17 +556,19 @@ int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest, c
   if (dim_a1 == 0) return accumulate ? B200GMM_OK : B200GMM_EINVAL;
   return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
                   workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr,
-                  row_weight, accumulate ? 1 : 0);
+                  row_weight, accumulate ? 1 : 0, dest_base, dest_bytes);
 }
 
 int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index, const void* b, void* c,
-                       const int64_t* row_dest, const int64_t* batch_sizes, int batch_sizes_on_device,
+                       const int64_t* row_dest, const void* dest_base, int64_t dest_bytes,
+                       const int64_t* batch_sizes, int batch_sizes_on_device,
                        int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b, void* workspace,
                        size_t workspace_bytes, uint32_t* device_status, void* cuda_stream) {
   if (row_index == nullptr || x_rows <= 0 || x_rows >= (int64_t(1) << 31)) return B200GMM_EINVAL;
   if (c == nullptr && row_dest == nullptr) return B200GMM_EINVAL;
   return run_impl(x, b, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
-                  workspace_bytes, device_status, cuda_stream, row_dest, row_index, x_rows);
+                  workspace_bytes, device_status, cuda_stream, row_dest, row_index, x_rows, nullptr, nullptr, 0,
+                  dest_base, dest_bytes);
 }
 
 int b200gmm_run_gather_wgrad(const void* x, int64_t x_rows, const int32_t* row_index, const void* grad, void* c,
@@ -519,16 +581,18 @@ int b200gmm_run_gather_wgrad(const void* x, int64_t x_rows, const int32_t* row_i
 }
 
 int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void* c, const int64_t* row_dest,
-                       const int64_t* batch_sizes, int batch_sizes_on_device, int z, int64_t tokens,
+                       const void* dest_base, int64_t dest_bytes, const int64_t* batch_sizes, int batch_sizes_on_device, int z, int64_t tokens,
                        int64_t dim_a1, int64_t n, int trans_b, void* workspace, size_t workspace_bytes,
                        uint32_t* device_status, void* cuda_stream) {
   if (c == nullptr && row_dest == nullptr) return B200GMM_EINVAL;
   if (b_up == nullptr && tokens > 0 && n > 0 && dim_a1 > 0 && z > 0) return B200GMM_EINVAL;
   if (b_up == nullptr || dim_a1 == 0)  // nothing to multiply: silu(0) * 0 = 0, the plain path's zeros
     return run_impl(a, b_gate, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
-                    workspace_bytes, device_status, cuda_stream, row_dest);
+                    workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr, nullptr, 0, dest_base,
+                    dest_bytes);
   return run_impl(a, b_gate, c, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b, workspace,
-                  workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, b_up);
+                  workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, b_up, nullptr, 0, dest_base,
+                  dest_bytes);
 }
 
 int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* batch_sizes,
@@ -575,15 +639,13 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a
   if (z > kMaxExperts) return B200GMM_ELIMIT;
   if (z == 0) return B200GMM_OK;
   if (batch_sizes_device == nullptr || out_device == nullptr) return B200GMM_EINVAL;
-  Problem p;
+  Problem p = {};
   p.mode = trans_a ? kTN : (trans_b ? kNT : kNN);
   p.z = z;
-  p.tokens = 0;
   p.d1 = dim_a1;
   p.n = n;
   p.tile_m = kBlockM;
   p.group_m = 1;
-  p.direct_store = 0;
   fill_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(batch_sizes_device, p,
                                                                             out_device);
   if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
@@ -599,28 +661,75 @@ int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z, int64_t tokens
   const int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, cluster_ctas, &p);
   if (rc != B200GMM_OK) return rc;
   if (n_tiles == nullptr || (z > 0 && batch_sizes_host == nullptr)) return B200GMM_EINVAL;
-  int64_t count = 0;
+  // The kernels' build_schedule, replayed: clamped row prefix sums, the order of
+  // the experts, tile prefix sums in that order.
+  std::vector<int> row_start(size_t(z) + 1), perm(static_cast<size_t>(z)), tile_start(size_t(z) + 1);
   int64_t start = 0;
   for (int e = 0; e < z; ++e) {
-    int64_t v = batch_sizes_host[e] < 0 ? 0 : batch_sizes_host[e];
-    int64_t s = start < tokens ? start : tokens;
-    int64_t en = (start + v) < tokens ? (start + v) : tokens;
-    start += v;
-    const int tiles = expert_tiles(p, en - s);
-    for (int l = 0; l < tiles; ++l) {
-      if (out != nullptr && count < max_tiles) {
-        const Tile t = make_tile(p, e, l, static_cast<int>(s), static_cast<int>(en));
-        int64_t* o = out + count * 5;
-        o[0] = t.expert;
-        o[1] = t.row0;
-        o[2] = t.col0;
-        o[3] = t.valid_rows;
-        o[4] = (t.k_len + kBlockK - 1) / kBlockK;
-      }
-      ++count;
-    }
+    row_start[e] = static_cast<int>(start < tokens ? start : tokens);
+    start += batch_sizes_host[e] < 0 ? 0 : batch_sizes_host[e];
   }
-  *n_tiles = count;
+  row_start[z] = static_cast<int>(start < tokens ? start : tokens);
+  for (int e = 0; e < z; ++e) perm[e] = e;
+  if (p.order)
+    std::stable_sort(perm.begin(), perm.end(), [&](int x, int y) {
+      return row_start[x + 1] - row_start[x] > row_start[y + 1] - row_start[y];
+    });
+  tile_start[0] = 0;
+  for (int i = 0; i < z; ++i)
+    tile_start[i + 1] = tile_start[i] + expert_tiles(p, row_start[perm[i] + 1] - row_start[perm[i]]);
+  const int total = tile_start[z];
+  int front = 0, back = z > 0 ? z - 1 : 0;
+  for (int t = 0; t < total && out != nullptr && t < max_tiles; ++t) {
+    int stream;
+    const int q = order_index(p.order, t, total, &stream);
+    int pos;
+    if (stream == 0) {
+      while (q >= tile_start[front + 1]) ++front;
+      pos = front;
+    } else {
+      while (q < tile_start[back]) --back;
+      pos = back;
+    }
+    const int e = perm[pos];
+    const Tile tile = make_tile(p, e, q - tile_start[pos], row_start[e], row_start[e + 1]);
+    int64_t* o = out + int64_t(t) * B200GMM_SCHEDULE_FIELDS;
+    o[0] = tile.expert;
+    o[1] = tile.row0;
+    o[2] = tile.col0;
+    o[3] = tile.valid_rows;
+    o[4] = tile_stages(tile);
+    o[5] = tile.kind;
+  }
+  *n_tiles = total;
+  return B200GMM_OK;
+}
+
+int b200gmm_schedule_device(const int64_t* batch_sizes_device, int z, int64_t tokens, int64_t dim_a1,
+                            int64_t n, int trans_a, int trans_b, int cluster_ctas, int32_t* out_device,
+                            int64_t max_tiles, int32_t* n_tiles_device, uint32_t* device_status,
+                            void* cuda_stream) {
+  Problem p;
+  if (cluster_ctas == 0) cluster_ctas = choose_ctas(z, tokens, dim_a1, trans_a);
+  const int rc = check_problem(z, tokens, dim_a1, n, trans_a, trans_b, cluster_ctas, &p);
+  if (rc != B200GMM_OK) return rc;
+  if (n_tiles_device == nullptr || (z > 0 && batch_sizes_device == nullptr) || max_tiles < 0 ||
+      max_tiles >= (int64_t(1) << 31) || (max_tiles > 0 && out_device == nullptr))
+    return B200GMM_EINVAL;
+  schedule_dump_kernel<<<1, kThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      batch_sizes_device, p, out_device, static_cast<int>(max_tiles), n_tiles_device, device_status);
+  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200GMM_OK;
+}
+
+int b200gmm_selftest_wait_timeout(int64_t limit_ns, uint32_t* device_status, void* cuda_stream) {
+  // A limit beyond a tenth of a second would only hold the GPU for nothing.
+  if (limit_ns <= 0 || limit_ns > 100000000 || device_status == nullptr) return B200GMM_EINVAL;
+  wait_timeout_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(static_cast<uint64_t>(limit_ns),
+                                                                           device_status);
+  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
   return B200GMM_OK;
 }
 

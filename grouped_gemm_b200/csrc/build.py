@@ -57,11 +57,15 @@ def build(force=False, verbose=False):
     return LIB
 
 
-EXT_NAME = "b200gmm_torch_binding"
+# The torch extension carries the name of the reference's compiled module
+# (setup.py:35 and grouped_gemm/backend.py:8 there) and is put beside the packages,
+# so that ``import grouped_gemm_backend`` finds it the way it finds the reference's.
+EXT_NAME = "grouped_gemm_backend"
 EXT_DIR = os.path.join(HERE, "torch_ext")
 EXT_SRC = os.path.join(EXT_DIR, "binding.cpp")
 EXT_BUILD = os.path.join(EXT_DIR, "build")
-EXT_LIB = os.path.join(EXT_BUILD, EXT_NAME + ".so")
+EXT_BUILT = os.path.join(EXT_BUILD, EXT_NAME + ".so")
+EXT_LIB = os.path.join(ROOT, EXT_NAME + ".so")
 
 
 def binding_is_stale():
@@ -74,7 +78,8 @@ def binding_is_stale():
 def build_torch_binding(force=False, verbose=False):
     """Compile the torch extension module (torch_ext/binding.cpp) in-tree.  It is
     plain C++ (no device code): argument checks, stream and workspace from torch,
-    then the C ABI of libb200gmm.so, which it finds through its rpath."""
+    then the C ABI of libb200gmm.so, which it finds through its rpath (relative
+    to its own place beside the ``grouped_gemm_b200`` package)."""
     if not force and not binding_is_stale():
         return EXT_LIB
     build(force=False, verbose=verbose)  # the extension links against the library
@@ -82,10 +87,11 @@ def build_torch_binding(force=False, verbose=False):
     os.makedirs(EXT_BUILD, exist_ok=True)
     load(name=EXT_NAME, sources=[EXT_SRC], extra_include_paths=[os.path.join(ROOT, "include")],
          extra_cflags=["-O2", "-std=c++17"],
-         extra_ldflags=["-L" + HERE, "-lb200gmm", "-Wl,-rpath,$ORIGIN/../..", "-Wl,-rpath," + HERE],
+         extra_ldflags=["-L" + HERE, "-lb200gmm", "-Wl,-rpath,$ORIGIN/grouped_gemm_b200/csrc", "-Wl,-rpath," + HERE],
          build_directory=EXT_BUILD, with_cuda=True, verbose=verbose, is_python_module=False)
-    if not os.path.exists(EXT_LIB):
-        raise RuntimeError("torch extension build did not produce " + EXT_LIB)
+    if not os.path.exists(EXT_BUILT):
+        raise RuntimeError("torch extension build did not produce " + EXT_BUILT)
+    shutil.copy2(EXT_BUILT, EXT_LIB)
     os.utime(EXT_LIB, None)
     return EXT_LIB
 

@@ -1,7 +1,7 @@
 // The persistent grouped-GEMM kernel for sm_100a.
 //
-// One CTA per SM walks a static round-robin share of all experts' output tiles
-// (schedule.cuh).  Inside a CTA three roles run concurrently:
+// One CTA per SM works through the output tiles of all experts (schedule.cuh).
+// Inside a CTA three roles run concurrently:
 //   warp 0      TMA producer: fills a ring of {A tile, B tile} stages in shared
 //               memory (128-byte swizzle), one mbarrier per stage;
 //   warp 1      MMA issuer: one lane issues tcgen05.mma (bf16 x bf16 -> fp32 in
@@ -14,10 +14,17 @@
 //               the current one is converted), rounds to bf16, stages the 32x32
 //               chunk in swizzled shared memory and writes it with a TMA tensor
 //               store; a warp whose 32 rows do not all exist (ragged last tile of
-//               an expert) stores its valid rows directly.
+//               an expert) stores its valid rows directly;
+//   warp 10     scheduler (leader CTA): draws tile positions from a global counter,
+//               several tiles ahead of the other roles, and hands them over through
+//               a small ring in shared memory (in both CTAs of a pair); for wgrad
+//               it also prepares, ahead of time, the tensor maps clipped to the
+//               expert a tile belongs to.
 //
 // Two variants, chosen on the host:
-//   CTAS == 1   every CTA owns 128 x 256 output tiles (4 stages of 48 KiB);
+//   CTAS == 1   every CTA owns 128 x 256 output tiles (4 stages of 48 KiB).  The
+//               last <= 64 rows of an expert run as a transposed tile instead: 128
+//               output columns on UMMA M, the rows on UMMA N (schedule.cuh);
 //   CTAS == 2   a pair of CTAs (a 2-CTA cluster on neighbouring SMs) owns
 //               256 x 256 tiles: each CTA stages its own 128 rows of A and HALF of
 //               the B tile, and the leader's tcgen05.mma.cta_group::2 reads both
@@ -52,19 +59,23 @@
 namespace b200gmm {
 
 constexpr int kEpilogueWarps = 8;
-constexpr int kThreads = 32 * (2 + kEpilogueWarps);  // 320
+constexpr int kSchedWarp = 2 + kEpilogueWarps;        // warp 10
+constexpr int kThreads = 32 * (kSchedWarp + 1);       // 352
 constexpr int kMaxExperts = 1024;
 constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 6;
-static_assert(8 > kMaxStages, "kMapSlots must exceed the number of pipeline stages");
 constexpr uint32_t kBoxBytes = 64 * kBlockK * 2;  // one 64-wide MN-major TMA box: 8 KiB
 // wgrad keeps private, editable copies of its two tensor maps in the caller's
-// workspace: kMapSlots {a, b} pairs per CTA, used round-robin.  A slot is edited
-// again only after kMapSlots further edits, each followed by at least one load,
-// i.e. after more loads than the ring has stages, so no load still in flight
-// reads a map while it changes.
+// workspace: kMapSlots {a, b} pairs per cluster.  The scheduler edits a slot only
+// when it is not the current map of one of the two tile streams and every tile that
+// used it has all its loads landed (the MMA warp counts finished tiles).
 constexpr int kMapSlots = 8;
 constexpr int kMaxCtas = 256;  // workspace is sized for this many CTAs
+// Ring through which the scheduler hands tile positions to the other roles.  Deep
+// enough that the producer can run ahead by a ring of one-stage tiles plus both
+// accumulators, and that the scheduler's own latencies (the counter's round trip,
+// a tensor-map edit) stay hidden behind tiles already handed out.
+constexpr int kSchedSlots = 8;
 
 // wgrad gives up one ring stage for a second epilogue staging buffer per warp: its
 // tiles can be a single k-block deep (few rows per expert, or none), and then the
@@ -81,8 +92,17 @@ struct Geometry {
   static constexpr uint32_t kOutBytes = kEpilogueWarps * kOutBufs * 2048u;  // 16 KiB (wgrad: 32 KiB)
 };
 
+// A transposed tile's stage inside a one-CTA ring slot: 128 columns x 128 k of the
+// weights (32 KiB: two k-halves of 16 KiB) followed by up to 64 rows x 128 k of
+// the activations (two k-halves of 8 KiB).
+constexpr uint32_t kLightWBytes = kLightCols * kLightK * 2;        // 32 KiB
+constexpr uint32_t kLightWHalf = kLightWBytes / 2;                 // 16 KiB per 64 of k
+constexpr uint32_t kLightXHalf = kLightRows * kBlockK * 2;         // 8 KiB per 64 of k
+constexpr uint32_t kLightXBox = 32 * kBlockK * 2;                  // one 32-row TMA box: 4 KiB
+static_assert(kLightWBytes + 2 * kLightXHalf <= Geometry<1>::kStageBytes, "a transposed stage must fit a ring slot");
+
 // The gather variant adds one warp per ring stage; each fetches the rows of A for
-// the k-blocks that land in its stage (512 threads for a CTA pair, 448 for one CTA).
+// the k-blocks that land in its stage.
 template <int CTAS, int MODE = kNN>
 constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS, MODE>::kStages; }
 
@@ -98,10 +118,16 @@ struct __align__(8) SmemTail {
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t sched_full[kSchedSlots];
+  uint64_t sched_empty[kSchedSlots];
+  int sched_tile[kSchedSlots];      // position of the launch order
+  int sched_map[kSchedSlots];       // wgrad: map slot of the tile (bit 30: freshly edited), else 0
+  uint32_t tiles_done;              // tiles of this cluster whose loads have all landed
   uint32_t tmem_base;
   uint32_t abort_flag;
-  int row_start[kMaxExperts + 1];
-  int tile_start[kMaxExperts + 1];
+  int row_start[kMaxExperts + 1];   // exclusive prefix sum of batch_sizes, by expert
+  int tile_start[kMaxExperts + 1];  // exclusive prefix sum of tile counts, by position in perm
+  uint16_t perm[kMaxExperts];       // expert at each position of the launch order
 };
 
 // One size for every instantiation: the largest layout (forward / dgrad).
@@ -113,67 +139,171 @@ static_assert(Geometry<1, kTN>::kRingBytes + Geometry<1, kTN>::kOutBytes <= Geom
               Geometry<2, kTN>::kRingBytes + Geometry<2, kTN>::kOutBytes <= Geometry<1>::kRingBytes + Geometry<1>::kOutBytes,
               "the wgrad layout must fit the common size");
 
-// Exclusive prefix sums of batch_sizes (rows) and of per-expert tile counts,
-// by one warp, 32 experts per step with a running carry.  Rows are clamped to
-// `tokens` so that a bad batch_sizes can never push a store out of bounds.
-__device__ __forceinline__ void scan_batch_sizes(const Problem& p, const int64_t* batch_sizes,
-                                                 int* row_start, int* tile_start, uint32_t* status,
-                                                 int lane) {
-  int64_t carry_rows = 0;
-  int carry_tiles = 0;
-  uint32_t flags = 0;
-  for (int base = 0; base < p.z; base += 32) {
-    const int e = base + lane;
-    int64_t v = (e < p.z) ? batch_sizes[e] : 0;
-    if (v < 0) { v = 0; flags |= 0x2u; }
-    int64_t incl = v;
+// Inclusive prefix sum across the warp.
+template <typename T>
+__device__ __forceinline__ T warp_inclusive_scan(T v, int lane) {
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += up;
-    }
-    int64_t start = carry_rows + incl - v;
-    int64_t end = start + v;
-    if (end > p.tokens) { flags |= 0x4u; end = p.tokens; }
-    if (start > p.tokens) start = p.tokens;
-    const int tiles = (e < p.z) ? expert_tiles(p, end - start) : 0;
-    int incl_t = tiles;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, incl_t, d);
-      if (lane >= d) incl_t += up;
-    }
-    if (e < p.z) {
-      row_start[e] = static_cast<int>(start);
-      tile_start[e] = carry_tiles + incl_t - tiles;
-    }
-    carry_rows += __shfl_sync(0xffffffffu, incl, 31);
-    carry_tiles += __shfl_sync(0xffffffffu, incl_t, 31);
+  for (int d = 1; d < 32; d <<= 1) {
+    const T up = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= d) v += up;
   }
-  if (lane == 0) {
-    row_start[p.z] = static_cast<int>(carry_rows < p.tokens ? carry_rows : p.tokens);
-    tile_start[p.z] = carry_tiles;
-  }
-  flags = __reduce_or_sync(0xffffffffu, flags);
-  if (flags != 0u && lane == 0 && status != nullptr && blockIdx.x == 0) atomicOr(status, flags);
+  return v;
 }
 
-// Round-robin walk over this CTA's (or CTA pair's) tiles; every role keeps its own copy.
+// One step of the exclusive prefix sum of batch_sizes: the 32 experts base ..
+// base + 31 (zeros past z), added to the running carry.  Returns this lane's
+// exclusive sum and advances the carry.  The scan every kernel of this library
+// runs, whether it feeds the tile schedule or the exported argument fill.
+__device__ __forceinline__ int64_t scan_step(int64_t v, int lane, int64_t* carry) {
+  const int64_t incl = warp_inclusive_scan(v, lane);
+  const int64_t start = *carry + incl - v;
+  *carry += __shfl_sync(0xffffffffu, incl, 31);
+  return start;
+}
+
+// The schedule of one launch, built in shared memory by every CTA for itself
+// (all threads of the CTA must call this; it synchronises them):
+//   row_start   exclusive prefix sums of batch_sizes (int64 arithmetic, 32 experts
+//               per step with a running carry); rows are clamped to `tokens` so
+//               that a bad batch_sizes can never push a store out of bounds;
+//   perm        the experts in launch order: by index, or (order == 1) by number
+//               of rows, largest first, ties by index (the reference sorts its
+//               wgrad problems the same way, csrc/fill_arguments.cuh:80-86);
+//   tile_start  exclusive prefix sums of the per-expert tile counts in that order.
+__device__ __forceinline__ void build_schedule(const Problem& p, const int64_t* __restrict__ batch_sizes,
+                                               SmemTail* tail, uint32_t* status) {
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int scan_warp = (blockDim.x >= 96) ? 2 : 0;
+  int* row_start = tail->row_start;
+  if (warp == scan_warp) {
+    int64_t carry = 0;
+    uint32_t flags = 0;
+    for (int base = 0; base < p.z; base += 32) {
+      const int e = base + lane;
+      int64_t v = (e < p.z) ? batch_sizes[e] : 0;
+      if (v < 0) { v = 0; flags |= 0x2u; }
+      int64_t start = scan_step(v, lane, &carry);
+      if (start + v > p.tokens) flags |= 0x4u;
+      if (start > p.tokens) start = p.tokens;
+      if (e < p.z) row_start[e] = static_cast<int>(start);
+    }
+    if (lane == 0) row_start[p.z] = static_cast<int>(carry < p.tokens ? carry : p.tokens);
+    flags = __reduce_or_sync(0xffffffffu, flags);
+    if (flags != 0u && lane == 0 && status != nullptr && blockIdx.x == 0) atomicOr(status, flags);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < p.z; e += blockDim.x) {
+    int rank = e;
+    if (p.order) {
+      const int mine = row_start[e + 1] - row_start[e];
+      rank = 0;
+      int prev = row_start[0];
+      for (int j = 0; j < p.z; ++j) {
+        const int next = row_start[j + 1];
+        const int rj = next - prev;
+        prev = next;
+        rank += (rj > mine) ? 1 : 0;
+        rank += (rj == mine && j < e) ? 1 : 0;
+      }
+    }
+    tail->perm[rank] = static_cast<uint16_t>(e);
+  }
+  __syncthreads();
+  if (warp == scan_warp) {
+    int carry = 0;
+    for (int base = 0; base < p.z; base += 32) {
+      const int pos = base + lane;
+      int tiles = 0;
+      if (pos < p.z) {
+        const int e = tail->perm[pos];
+        tiles = expert_tiles(p, row_start[e + 1] - row_start[e]);
+      }
+      const int incl = warp_inclusive_scan(tiles, lane);
+      if (pos < p.z) tail->tile_start[pos] = carry + incl - tiles;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) tail->tile_start[p.z] = carry;
+  }
+}
+
+// Position of the launch order -> tile.  Every role keeps its own copy; positions
+// arrive in increasing order, so the expert cursors of the two streams (front of
+// the order, back of the order) only ever move one way.
 struct TileWalker {
   const Problem& p;
-  const int* row_start;
-  const int* tile_start;
-  int t;
-  int e;
+  const SmemTail* tail;
   int total;
-  int step;
-  __device__ TileWalker(const Problem& p_, const int* rs, const int* ts, int first, int stride)
-      : p(p_), row_start(rs), tile_start(ts), t(first), e(0), total(ts[p_.z]), step(stride) {}
-  __device__ __forceinline__ bool next(Tile* out) {
-    if (t >= total) return false;
-    while (t >= tile_start[e + 1]) ++e;
-    *out = make_tile(p, e, t - tile_start[e], row_start[e], row_start[e + 1]);
-    t += step;
+  int pos_front;
+  int pos_back;
+  __device__ TileWalker(const Problem& p_, const SmemTail* tail_)
+      : p(p_), tail(tail_), total(tail_->tile_start[p_.z]), pos_front(0), pos_back(p_.z > 0 ? p_.z - 1 : 0) {}
+  __device__ __forceinline__ bool decode(int t, Tile* out) {
+    if (t < 0 || t >= total) return false;
+    int stream;
+    const int q = order_index(p.order, t, total, &stream);
+    int pos;
+    if (stream == 0) {
+      while (q >= tail->tile_start[pos_front + 1]) ++pos_front;
+      pos = pos_front;
+    } else {
+      while (q < tail->tile_start[pos_back]) --pos_back;
+      pos = pos_back;
+    }
+    const int e = tail->perm[pos];
+    *out = make_tile(p, e, q - tail->tile_start[pos], tail->row_start[e], tail->row_start[e + 1]);
+    out->stream = stream;
+    return true;
+  }
+};
+
+// Where a role's tile positions come from: the leader CTA's scheduler thread
+// publishes each position (and, for wgrad, the tile's map slot) through
+// sched_tile / sched_map / sched_full, in its own CTA and in its peer; every other
+// role takes them from there and releases the slot on the leader's sched_empty.
+constexpr int kNoTile = -1;  // a wait was abandoned
+constexpr int kMapFresh = 1 << 30;  // sched_map flag: the slot was edited for this tile
+
+template <bool kPair>
+struct TileFeed {
+  SmemTail* tail;
+  ptx::WaitCtx wait;
+  uint32_t taken;   // positions taken (or published) so far
+  int map;          // sched_map entry of the position taken last
+
+  __device__ TileFeed(SmemTail* tail_, const ptx::WaitCtx& w) : tail(tail_), wait(w), taken(0), map(0) {}
+
+  // Consumer side, called by every lane of a warp (warp_wide) or by one thread.
+  __device__ __forceinline__ int take(bool warp_wide, int lane) {
+    const uint32_t slot = taken % kSchedSlots;
+    const uint32_t parity = (taken / kSchedSlots) & 1u;
+    ++taken;
+    if (!ptx::mbar_wait<kPair, 32>(ptx::smem_u32(&tail->sched_full[slot]), parity, wait)) return kNoTile;
+    const int t = *reinterpret_cast<volatile int*>(&tail->sched_tile[slot]);
+    map = *reinterpret_cast<volatile int*>(&tail->sched_map[slot]);
+    if (warp_wide) __syncwarp();
+    if (!warp_wide || lane == 0) {
+      const uint32_t bar = ptx::smem_u32(&tail->sched_empty[slot]);
+      if (kPair) ptx::mbar_arrive_release_cluster(ptx::mapa(bar, 0));
+      else ptx::mbar_arrive(bar);
+    }
+    return t;
+  }
+
+  // Scheduler side (one thread of the leader CTA): hand position t to everyone.
+  __device__ __forceinline__ bool publish(int t, int map_entry) {
+    const uint32_t slot = taken % kSchedSlots;
+    const uint32_t parity = (taken / kSchedSlots) & 1u;
+    ++taken;
+    if (!ptx::mbar_wait<kPair, 0>(ptx::smem_u32(&tail->sched_empty[slot]), parity ^ 1u, wait)) return false;
+    *reinterpret_cast<volatile int*>(&tail->sched_tile[slot]) = t;
+    *reinterpret_cast<volatile int*>(&tail->sched_map[slot]) = map_entry;
+    ptx::mbar_arrive(ptx::smem_u32(&tail->sched_full[slot]));
+    if (kPair) {
+      ptx::st_shared_cluster_u32(ptx::mapa(ptx::smem_u32(&tail->sched_tile[slot]), 1), static_cast<uint32_t>(t));
+      ptx::st_shared_cluster_u32(ptx::mapa(ptx::smem_u32(&tail->sched_map[slot]), 1), static_cast<uint32_t>(map_entry));
+      ptx::mbar_arrive_release_cluster(ptx::mapa(ptx::smem_u32(&tail->sched_full[slot]), 1));
+    }
     return true;
   }
 };
@@ -181,11 +311,13 @@ struct TileWalker {
 template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
 __global__ void __launch_bounds__(GATHER ? gather_threads<CTAS, MODE>() : kThreads, 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-           const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c, __nv_bfloat16* __restrict__ c,
+           const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
+           const __grid_constant__ CUtensorMap map_a2, __nv_bfloat16* __restrict__ c,
            const int64_t* __restrict__ batch_sizes, const Problem p,
-           uint32_t* status, CUtensorMap* map_slots, const int64_t* __restrict__ row_dest,
+           uint32_t* status, CUtensorMap* map_slots, uint32_t* sched_counter, const int64_t* __restrict__ row_dest,
            const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
-           const int64_t a_src_rows, const float* __restrict__ row_scale, const int reduce_add) {
+           const int64_t a_src_rows, const float* __restrict__ row_scale, const int reduce_add,
+           const int64_t dest_lo, const int64_t dest_hi) {
   static_assert(!SWIGLU || MODE != kTN, "the gated product is a forward product");
   // SWIGLU: two right operands of n columns each, b (gate) and b2 (up).  The
   // schedule runs over 2n virtual columns, 256 per tile: accumulator columns
@@ -195,6 +327,10 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   using G = Geometry<CTAS, MODE>;
   constexpr int kStages = G::kStages;
   constexpr bool kPair = (CTAS == 2);
+  // Transposed tiles exist in the plain one-CTA forward / dgrad kernels only
+  // (map_a2: the activations with 32-row boxes; NT also uses map_b2: b with
+  // 128-row boxes).
+  constexpr bool kLight = (MODE != kTN) && (CTAS == 1) && !GATHER && !SWIGLU;
 
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -208,14 +344,15 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   const int lane = threadIdx.x & 31;
   const uint32_t cta_rank = kPair ? ptx::cluster_ctarank() : 0u;  // 0 = leader (issues the MMAs)
   const bool leader = (cta_rank == 0u);
-  volatile uint32_t* abort_flag = &tail->abort_flag;
+  const ptx::WaitCtx wait{&tail->abort_flag, static_cast<uint64_t>(p.wait_ns)};
 
   // ------------------------------------------------------------ prologue
   if (warp == 0) {
     if (lane == 0) {
       ptx::prefetch_tensormap(&map_a);
       ptx::prefetch_tensormap(&map_b);
-      if (SWIGLU) ptx::prefetch_tensormap(&map_b2);
+      if (SWIGLU || (kLight && MODE == kNT)) ptx::prefetch_tensormap(&map_b2);
+      if (kLight) ptx::prefetch_tensormap(&map_a2);
       ptx::prefetch_tensormap(&map_c);
       for (int s = 0; s < kStages; ++s) {
         // the producer's expect_tx arrival, plus one arrival by the gather warp that owns
@@ -227,6 +364,14 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[i]), 1);
         ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[i]), kEpilogueWarps * CTAS);
       }
+      // Takers of a published tile position: per CTA the producer thread, the epilogue
+      // warps and the gather warps, plus the leader's MMA warp.
+      constexpr uint32_t kTakers = CTAS * (1 + kEpilogueWarps + (GATHER ? kStages : 0)) + 1;
+      for (int i = 0; i < kSchedSlots; ++i) {
+        ptx::mbar_init(ptx::smem_u32(&tail->sched_full[i]), 1);
+        ptx::mbar_init(ptx::smem_u32(&tail->sched_empty[i]), kTakers);
+      }
+      tail->tiles_done = 0u;
       tail->abort_flag = 0u;
       ptx::fence_mbar_init();
     }
@@ -239,9 +384,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), kTmemCols);
       ptx::tmem_relinquish();
     }
-  } else if (warp == 2) {
-    scan_batch_sizes(p, batch_sizes, tail->row_start, tail->tile_start, status, lane);
   }
+  build_schedule(p, batch_sizes, tail, status);
   ptx::tc_fence_before_sync();
   __syncthreads();
   if (kPair) ptx::cluster_sync();  // the peer's barriers exist before anything arrives on them
@@ -258,51 +402,69 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   const int row_off = static_cast<int>(cta_rank) * kBlockM;  // this CTA's rows inside a pair tile
   const int col_off = static_cast<int>(cta_rank) * G::kBCols;  // this CTA's share of the B tile
 
+  // wgrad: the editable copies of the two tensor maps, one set per cluster (both
+  // CTAs of a pair load through the same copies).
+  CUtensorMap* my_maps = map_slots + size_t(first_tile) * (kMapSlots * 2);
+
   if (warp == 0) {
     // ---------------------------------------------------------- TMA producer
-    CUtensorMap* my_maps = map_slots + size_t(blockIdx.x) * (kMapSlots * 2);
-    if (MODE == kTN) {
-      // Private copies of both maps in every slot (2 KiB per CTA), by the whole warp.
-      const uint4* src_a = reinterpret_cast<const uint4*>(&map_a);
-      const uint4* src_b = reinterpret_cast<const uint4*>(&map_b);
-      uint4* dst = reinterpret_cast<uint4*>(my_maps);
-      for (int i = lane; i < kMapSlots * 2 * 8; i += 32) {
-        const int which = (i >> 3) & 1;  // 8 x 16 bytes per map; maps alternate a, b
-        dst[i] = which ? src_b[i & 7] : src_a[i & 7];
-      }
-      __syncwarp();
-    }
     if (lane == 0) {
-      TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+      TileWalker walk(p, tail);
+      TileFeed<kPair> feed(tail, wait);
       Tile t;
       uint32_t s = 0, ph = 0;
       bool ok = true;
-      int slot = 0, slot_expert = -1;
       // Bytes this CTA's TMA loads bring per stage: the gather warps fetch A themselves.
       constexpr uint32_t kTmaBytes = GATHER ? G::kBBytes : G::kStageBytes;
       const CUtensorMap* tn_a = my_maps;
       const CUtensorMap* tn_b = my_maps + 1;
-      while (ok && walk.next(&t)) {
-        const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
-        if (MODE == kTN && nkb > 0 && t.expert != slot_expert) {
-          // New expert: clip the row extent of a and b at its last row, so that
-          // the rows a k-block would read from the next expert are out of bounds
-          // for TMA and arrive as zeros.
-          slot_expert = t.expert;
-          slot = (slot + 1) % kMapSlots;
-          CUtensorMap* ea = my_maps + slot * 2;
-          CUtensorMap* eb = ea + 1;
-          const uint32_t rows_end = static_cast<uint32_t>(t.k_row0 + t.k_len);
-          ptx::tensormap_set_dim1(ea, rows_end);
-          ptx::tensormap_set_dim1(eb, rows_end);
-          ptx::fence_tensormap_release();
-          ptx::fence_tensormap_acquire(ea);
-          ptx::fence_tensormap_acquire(eb);
-          tn_a = ea;
-          tn_b = eb;
+      while (ok) {
+        const int pos = feed.take(false, 0);
+        if (pos == kNoTile) { ok = false; break; }
+        if (!walk.decode(pos, &t)) break;
+        const int nkb = tile_stages(t);
+        if (kLight && t.kind) {
+          // Transposed tile: per stage 128 columns x 128 k of b[expert] (the UMMA A
+          // operand) and the tile's rows x 128 k of a (the UMMA B operand, K-major,
+          // fetched in boxes of 32 rows; rows past the tile's last are never stored).
+          const int row_boxes = (t.valid_rows + 31) >> 5;
+          const uint32_t bytes = kLightWBytes + 2u * uint32_t(row_boxes) * kLightXBox;
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, wait)) { ok = false; break; }
+            const uint32_t bar = ptx::smem_u32(&tail->full[s]);
+            const uint32_t sw = stage_base + s * G::kStageBytes;
+            const uint32_t sx = sw + kLightWBytes;
+            ptx::mbar_arrive_expect_tx(bar, bytes);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const int k0 = kb * kLightK + h * kBlockK;
+              if (MODE == kNN) {
+                ptx::tma_load_3d(sw + h * kLightWHalf, &map_b, bar, t.col0, k0, t.expert);
+                ptx::tma_load_3d(sw + h * kLightWHalf + kBoxBytes, &map_b, bar, t.col0 + 64, k0, t.expert);
+              } else {
+                ptx::tma_load_3d(sw + h * kLightWHalf, &map_b2, bar, k0, t.col0, t.expert);
+              }
+              for (int i = 0; i < row_boxes; ++i)
+                ptx::tma_load_2d(sx + h * kLightXHalf + i * kLightXBox, &map_a2, bar, k0, t.row0 + i * 32);
+            }
+            if (++s == kStages) { s = 0; ph ^= 1u; }
+          }
+          continue;
+        }
+        if (MODE == kTN && nkb > 0) {
+          // The scheduler clipped a copy of both maps at this expert's last row, so
+          // that the rows a k-block would read from the next expert are out of bounds
+          // for TMA and arrive as zeros.  A freshly edited copy has to be acquired by
+          // the thread that loads through it.
+          tn_a = my_maps + (feed.map & (kMapSlots - 1)) * 2;
+          tn_b = tn_a + 1;
+          if (feed.map & kMapFresh) {
+            ptx::fence_tensormap_acquire(tn_a);
+            ptx::fence_tensormap_acquire(tn_b);
+          }
         }
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(ptx::smem_u32(&tail->empty[s]), ph ^ 1u, wait)) { ok = false; break; }
           const uint32_t local_bar = ptx::smem_u32(&tail->full[s]);
           const uint32_t sa = stage_base + s * G::kStageBytes;
           const uint32_t sb = sa + G::kABytes;
@@ -372,22 +534,61 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     __syncwarp();
   } else if (warp == 1 && leader) {
     // ---------------------------------------------------------- MMA issuer
-    TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+    TileWalker walk(p, tail);
+    TileFeed<kPair> feed(tail, wait);
     Tile t;
     uint32_t s = 0, ph = 0, it = 0;
     bool ok = true;
-    while (ok && walk.next(&t)) {
-      const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
-      if (nkb == 0) continue;  // empty wgrad expert: the epilogue writes zeros
+    // Tells the scheduler how many tiles have all their loads landed (it may then
+    // edit the tensor-map copies those tiles loaded through).
+    auto loads_landed = [&]() {
+      if (MODE == kTN && lane == 0) *reinterpret_cast<volatile uint32_t*>(&tail->tiles_done) = feed.taken;
+    };
+    while (ok) {
+      const int pos = feed.take(true, lane);
+      if (pos == kNoTile) { ok = false; break; }
+      if (!walk.decode(pos, &t)) break;
+      const int nkb = tile_stages(t);
+      if (nkb == 0) { loads_landed(); continue; }  // empty wgrad expert: the epilogue writes zeros
       const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
       ++it;
       const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
-      if (!ptx::mbar_wait(te_bar, aph ^ 1u, abort_flag)) { ok = false; break; }
+      if (!ptx::mbar_wait(te_bar, aph ^ 1u, wait)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + ab * kBlockN;
+      if (kLight && t.kind) {
+        // D[128 output columns, rows rounded up to 16] = W[128, k] x X[rows, k]^T
+        const int n_mma = (t.valid_rows + 15) & ~15;
+        const uint32_t idesc = ptx::make_idesc_bf16(kLightCols, n_mma, MODE == kNN ? 1 : 0, 0);
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!ptx::mbar_wait(ptx::smem_u32(&tail->full[s]), ph, wait)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t sw = stage_base + s * G::kStageBytes;
+          const uint32_t sx = sw + kLightWBytes;
+          if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < kLightK / 16; ++k) {
+              const int h = k >> 2, j = k & 3;
+              // NN: b[k, n] tile is MN-major (64-column boxes 8 KiB apart, +2048 B per
+              // 16 of k); NT: b[n, k] tile is K-major (+32 B per 16 of k).
+              const uint64_t adesc = (MODE == kNN)
+                  ? ptx::make_smem_desc(sw + h * kLightWHalf, kBoxBytes, 1024u) + uint64_t(j) * (2048u >> 4)
+                  : ptx::make_smem_desc(sw + h * kLightWHalf, 16u, 1024u) + uint64_t(j) * (32u >> 4);
+              const uint64_t bdesc = ptx::make_smem_desc(sx + h * kLightXHalf, 16u, 1024u) + uint64_t(j) * (32u >> 4);
+              ptx::mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            ptx::mma_commit(ptx::smem_u32(&tail->empty[s]));
+          }
+          __syncwarp();
+          if (++s == kStages) { s = 0; ph ^= 1u; }
+        }
+        if (ok && lane == 0) ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[ab]));
+        __syncwarp();
+        continue;
+      }
       for (int kb = 0; kb < nkb; ++kb) {
         const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
-        if (!ptx::mbar_wait(f_bar, ph, abort_flag)) { ok = false; break; }
+        if (!ptx::mbar_wait(f_bar, ph, wait)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t sa = stage_base + s * G::kStageBytes;
         const uint32_t sb = sa + G::kABytes;
@@ -416,6 +617,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         __syncwarp();
         if (++s == kStages) { s = 0; ph ^= 1u; }
       }
+      if (ok) loads_landed();
       if (ok && lane == 0) {
         if (kPair) ptx::mma_commit_pair(ptx::smem_u32(&tail->tmem_full[ab]), 0x3);
         else ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[ab]));
@@ -424,7 +626,98 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
   } else if (warp == 1) {
     // peer CTA of a pair: the leader issues the MMAs for both
-  } else if (GATHER && warp >= 2 + kEpilogueWarps) {
+  } else if (warp == kSchedWarp) {
+    // ---------------------------------------------------------- scheduler
+    if (leader) {
+      if (MODE == kTN) {
+        // Copies of both maps in every slot (2 KiB per cluster), by the whole warp.
+        const uint4* src_a = reinterpret_cast<const uint4*>(&map_a);
+        const uint4* src_b = reinterpret_cast<const uint4*>(&map_b);
+        uint4* dst = reinterpret_cast<uint4*>(my_maps);
+        for (int i = lane; i < kMapSlots * 2 * 8; i += 32) {
+          const int which = (i >> 3) & 1;  // 8 x 16 bytes per map; maps alternate a, b
+          dst[i] = which ? src_b[i & 7] : src_a[i & 7];
+        }
+        __syncwarp();
+      }
+      if (lane == 0) {
+        TileWalker walk(p, tail);
+        TileFeed<kPair> feed(tail, wait);
+        Tile t;
+        // wgrad: the map slot and expert of each of the two tile streams, the slot
+        // edited last, and for every slot the index (in this cluster's sequence of
+        // tiles) of the last tile that loads through it.
+        int held_expert[2] = {-1, -1};
+        int held_slot[2] = {-1, -1};
+        int last_slot = 0;
+        int last_tile[kMapSlots];
+#pragma unroll
+        for (int i = 0; i < kMapSlots; ++i) last_tile[i] = -1;
+        int pos = first_tile;
+        // Positions after the first come from the global counter, drawn one tile
+        // ahead of their use so that the atomic's round trip is never waited for.
+        uint32_t drawn = (p.dynamic && pos < walk.total) ? atomicAdd(sched_counter, 1u) : 0u;
+        bool ok = true;
+        while (ok) {
+          int entry = 0;
+          const bool live = walk.decode(pos, &t);
+          if (MODE == kTN && live && t.k_len > 0) {
+            const int st = t.stream;
+            if (held_expert[st] != t.expert) {
+              // New expert on this stream: clip the row extent of a and b at its last
+              // row in a copy that neither stream uses and no unfinished tile loads
+              // through.  With kMapSlots copies one is free as soon as the MMA warp has
+              // caught up far enough; until then, wait (the tiles in question have been
+              // handed out already and finish on their own).
+              int slot = -1;
+              const uint64_t t0 = ptx::globaltimer_ns();
+              while (slot < 0) {
+                const int done = static_cast<int>(*reinterpret_cast<volatile uint32_t*>(&tail->tiles_done));
+                int cand = last_slot;
+#pragma unroll
+                for (int i = 0; i < kMapSlots; ++i) {
+                  cand = (cand + 1) % kMapSlots;
+                  if (slot < 0 && cand != held_slot[0] && cand != held_slot[1] && last_tile[cand] < done) slot = cand;
+                }
+                if (slot < 0) {
+                  if (tail->abort_flag || ptx::globaltimer_ns() - t0 > wait.limit_ns) {
+                    tail->abort_flag = 1u;
+                    ok = false;
+                    break;
+                  }
+                  __nanosleep(64);
+                }
+              }
+              if (!ok) break;
+              last_slot = slot;
+              held_expert[st] = t.expert;
+              held_slot[st] = slot;
+              CUtensorMap* ea = my_maps + slot * 2;
+              CUtensorMap* eb = ea + 1;
+              const uint32_t rows_end = static_cast<uint32_t>(t.k_row0 + t.k_len);
+              ptx::tensormap_set_dim1(ea, rows_end);
+              ptx::tensormap_set_dim1(eb, rows_end);
+              ptx::fence_tensormap_release();
+              entry = kMapFresh;
+            }
+            entry |= held_slot[st];
+#pragma unroll
+            for (int i = 0; i < kMapSlots; ++i)
+              if (i == held_slot[st]) last_tile[i] = static_cast<int>(feed.taken);
+          }
+          if (!feed.publish(pos, entry)) { ok = false; break; }
+          if (!live) break;  // the end of the order has been handed to everyone
+          if (p.dynamic) {
+            pos = static_cast<int>(drawn) + tile_stride;
+            if (pos < walk.total) drawn = atomicAdd(sched_counter, 1u);
+          } else {
+            pos += tile_stride;
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else if (GATHER && warp > kSchedWarp) {
     // ---------------------------------------------------------- A-row gather
     // The caller's sort-by-expert fused into the load: row i of the grouped
     // operand is row a_rows[i] of a_src (rows of p.d1 elements).  Gather warp w
@@ -436,21 +729,25 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     // one row, a lane serves rows sub, sub + 4, .. sub + 124, and writes the
     // K-major 128-byte-swizzled layout a TMA box load would leave (16-byte chunk
     // index ^= row % 8).
-    const int w = warp - (2 + kEpilogueWarps);  // the stage this warp owns
+    const int w = warp - (kSchedWarp + 1);  // the stage this warp owns
     const int chunk = lane & 7;
     const int sub = lane >> 3;
     const uint32_t stage_addr = stage_base + uint32_t(w) * G::kStageBytes;
     const uint32_t full_bar = kPair ? ptx::mapa(ptx::smem_u32(&tail->full[w]), 0) : ptx::smem_u32(&tail->full[w]);
     const uint32_t empty_bar = ptx::smem_u32(&tail->empty[w]);
-    TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+    TileWalker walk(p, tail);
+    TileFeed<kPair> feed(tail, wait);
     Tile t;
     uint32_t ph = 0;  // parity of this stage's current use
     int next = w;     // position in the stream of k-blocks of this warp's next one
     int base = 0;     // k-blocks of the stream before the current tile
     bool ok = true;
     bool bad_index = false;
-    while (ok && walk.next(&t)) {
-      const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+    while (ok) {
+      const int pos = feed.take(true, lane);
+      if (pos == kNoTile) { ok = false; break; }
+      if (!walk.decode(pos, &t)) break;
+      const int nkb = tile_stages(t);
       if (MODE == kTN) {
         // wgrad: the gathered rows are the contraction.  A k-block is 64 grouped rows
         // (k_row0 + 64 kb ..) by this CTA's 128 columns of a_src, staged as two
@@ -473,7 +770,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         };
         if (next < base + nkb) load_idx(next - base);
         for (; next < base + nkb; next += kStages) {
-          if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, abort_flag);
+          if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, wait);
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
 #pragma unroll
@@ -519,7 +816,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           }
         }
         for (; next < base + nkb; next += kStages) {
-          if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, abort_flag);
+          if (lane == 0) ok = ptx::mbar_wait(empty_bar, ph ^ 1u, wait);
           ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
           if (!ok) break;
           const int kcol = (next - base) * kBlockK + chunk * 8;
@@ -554,11 +851,19 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
     const int col_base = half * (kBlockN / 2);
     const uint32_t my_out = out_base + uint32_t(warp - 2) * (kStageOutBytes * G::kOutBufs);
-    TileWalker walk(p, tail->row_start, tail->tile_start, first_tile, tile_stride);
+    TileWalker walk(p, tail);
+    TileFeed<kPair> feed(tail, wait);
     Tile t;
     uint32_t it = 0;
     uint32_t stores = 0;  // TMA stores this warp has issued (lane 0's bulk groups)
     bool ok = true;
+    bool bad_dest = false;  // a row_dest entry outside the window the caller declared
+    // A scattered row may only go to a 16-byte aligned address inside [dest_lo, dest_hi)
+    // (dest_hi == 0: the caller vouches for its table, e.g. rows in a peer GPU's buffer).
+    const int64_t dest_row_bytes = (SWIGLU ? (p.n >> 1) : p.n) * 2;
+    auto dest_ok = [&](int64_t addr) {
+      return dest_hi == 0 || (addr >= dest_lo && addr + dest_row_bytes <= dest_hi && (addr & 15) == 0);
+    };
     // Buffer for the next TMA store and the wait before it may be written: with two
     // buffers the store before last read this one.
     auto stage_buf = [&]() { return my_out + (G::kOutBufs == 2 ? (stores & 1u) * kStageOutBytes : 0u); };
@@ -634,22 +939,79 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
     };
 
-    while (ok && walk.next(&t)) {
-      const int nkb = (t.k_len + kBlockK - 1) / kBlockK;
+    while (ok) {
+      const int pos = feed.take(true, lane);
+      if (pos == kNoTile) { ok = false; break; }
+      if (!walk.decode(pos, &t)) break;
+      const int nkb = tile_stages(t);
+      if (kLight && t.kind) {
+        // Transposed tile: TMEM lane = output column, TMEM column = output row.  This
+        // warp reads the 32 output columns of its lane quadrant for its half of the
+        // rows, eight rows at a time, and every lane writes its column of each row:
+        // a warp's store covers 64 consecutive bytes of one output row.  (The rows
+        // of all such tiles together are a sliver of the output.)
+        const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
+        ++it;
+        if (!ptx::mbar_wait<false, 64>(ptx::smem_u32(&tail->tmem_full[ab]), aph, wait)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const int n_mma = (t.valid_rows + 15) & ~15;
+        const int half_rows = n_mma >> 1;  // a multiple of 8
+        const int r_base = half * half_rows;
+        const int col = t.col0 + q * 32 + lane;
+        const bool col_ok = col < p.n;
+        const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN + uint32_t(r_base);
+        for (int i = 0; i < half_rows; i += 8) {
+          uint32_t v[8];
+          ptx::tmem_ld_32x8(taddr + uint32_t(i), v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const int r = r_base + i + u;
+            if (r < t.valid_rows && col_ok) {
+              const int64_t grow = int64_t(t.row0) + r;
+              float f = __uint_as_float(v[u]);
+              __nv_bfloat16* dst;
+              if (row_dest != nullptr) {
+                const int64_t addr = row_dest[grow];
+                if (!dest_ok(addr)) { bad_dest = true; continue; }
+                if (row_scale != nullptr) f *= row_scale[grow];
+                dst = reinterpret_cast<__nv_bfloat16*>(addr) + col;
+              } else {
+                dst = c + grow * p.n + col;
+              }
+              const __nv_bfloat16 h = __float2bfloat16_rn(f);
+              if (row_dest != nullptr && reduce_add) atomicAdd(dst, h);
+              else *dst = h;
+            }
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[ab]));
+        continue;
+      }
       const int r = row_off + q * 32 + lane;  // row inside the (pair) tile
-      const bool row_ok = r < t.valid_rows;
+      bool row_ok = r < t.valid_rows;
       // row_dest != nullptr (expert-parallel combine fused into this epilogue):
       // output row i does not go to c[i] but to the address row_dest[i], which may
       // be a row of a buffer on another GPU; such rows are written with plain
       // stores by the lane that holds them.
       const bool scatter = (MODE != kTN) && (row_dest != nullptr);
-      const bool warp_full = !p.direct_store && !scatter && (row_off + q * 32 + 31) < t.valid_rows;
+      const bool warp_full = !scatter && (row_off + q * 32 + 31) < t.valid_rows;
       const int64_t out_row0 = (MODE == kTN) ? (int64_t(t.expert) * p.d1 + t.row0) : int64_t(t.row0);
       // Output geometry: the gated product writes half as many columns as it schedules.
       const int64_t out_n = SWIGLU ? (p.n >> 1) : p.n;
       const int out_col0 = SWIGLU ? (t.col0 >> 1) : t.col0;
       __nv_bfloat16* crow = c + (out_row0 + r) * out_n + out_col0;
-      if (scatter && row_ok) crow = reinterpret_cast<__nv_bfloat16*>(row_dest[out_row0 + r]) + out_col0;
+      if (scatter && row_ok) {
+        const int64_t addr = row_dest[out_row0 + r];
+        if (dest_ok(addr)) {
+          crow = reinterpret_cast<__nv_bfloat16*>(addr) + out_col0;
+        } else {  // never written: skipped and reported
+          row_ok = false;
+          bad_dest = true;
+        }
+      }
       const int tile_row = static_cast<int>(out_row0) + row_off + q * 32;  // first row of this warp
       const int cols_left = static_cast<int>(out_n) - out_col0;  // multiple of 8
       // Scatter mode with per-row weights (the router's top-k weight of this row).
@@ -695,7 +1057,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
       ++it;
-      if (!ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[ab]), aph, abort_flag)) { ok = false; break; }
+      if (!ptx::mbar_wait<false, 64>(ptx::smem_u32(&tail->tmem_full[ab]), aph, wait)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       if (SWIGLU) {
         // This warp's 64 of the tile's 128 output columns: gate from accumulator
@@ -754,12 +1116,13 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
     // Shared memory must outlive the stores that still read it.
     if (lane == 0 || scatter_rows) ptx::bulk_wait_group_all();
+    if (bad_dest && status != nullptr) atomicOr(status, 0x10u);
     __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown
   __syncthreads();
-  if (*abort_flag) {
+  if (tail->abort_flag) {
     // A wait gave up.  Report it, then give copies and MMAs still in flight time
     // to land before shared memory and TMEM are handed back.
     if (threadIdx.x == 0 && status != nullptr) atomicOr(status, 0x1u);
@@ -777,8 +1140,9 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   }
 }
 
-// Argument fill on its own (bit-exact tests, inspection): same scan as above,
-// writes the reference's nine per-expert values (schedule.cuh: fill_fields).
+// Argument fill on its own (bit-exact tests, inspection): the same scan step the
+// GEMM kernels' schedule is built from, writing the reference's nine per-expert
+// values (schedule.cuh: fill_fields).
 __global__ void __launch_bounds__(32, 1)
 fill_offsets_kernel(const int64_t* __restrict__ batch_sizes, const Problem p, int64_t* __restrict__ out) {
   const int lane = threadIdx.x;
@@ -786,15 +1150,52 @@ fill_offsets_kernel(const int64_t* __restrict__ batch_sizes, const Problem p, in
   for (int base = 0; base < p.z; base += 32) {
     const int e = base + lane;
     const int64_t v = (e < p.z) ? batch_sizes[e] : 0;
-    int64_t incl = v;
-#pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-      const int64_t up = __shfl_up_sync(0xffffffffu, incl, d);
-      if (lane >= d) incl += up;
-    }
-    if (e < p.z) fill_fields(p, e, carry + incl - v, v, out + int64_t(e) * 9);
-    carry += __shfl_sync(0xffffffffu, incl, 31);
+    const int64_t start = scan_step(v, lane, &carry);
+    if (e < p.z) fill_fields(p, e, start, v, out + int64_t(e) * 9);
   }
+}
+
+// The schedule a GEMM launch with this Problem walks, written out for tests: runs
+// the kernels' own build_schedule and TileWalker in one CTA and stores, for every
+// position of the launch order, {expert, row0, col0, valid_rows, stages, kind}.
+// out_count receives the number of tiles; at most max_tiles are written.
+__global__ void __launch_bounds__(kThreads, 1)
+schedule_dump_kernel(const int64_t* __restrict__ batch_sizes, const Problem p, int32_t* __restrict__ out,
+                     int max_tiles, int32_t* __restrict__ out_count, uint32_t* status) {
+  __shared__ SmemTail tail;
+  build_schedule(p, batch_sizes, &tail, status);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    TileWalker walk(p, &tail);
+    Tile t;
+    int n = 0;
+    for (int pos = 0; walk.decode(pos, &t); ++pos) {
+      if (n < max_tiles) {
+        int32_t* o = out + int64_t(n) * 6;
+        o[0] = t.expert; o[1] = t.row0; o[2] = t.col0; o[3] = t.valid_rows; o[4] = tile_stages(t); o[5] = t.kind;
+      }
+      ++n;
+    }
+    *out_count = n;
+  }
+}
+
+// A wait that nothing ends, with the caller's limit: one warp waits on an mbarrier
+// nobody arrives on, gives up after limit_ns and reports STATUS_TIMEOUT exactly as
+// the GEMM kernels' roles do.  Nothing is in flight, so the launch ends cleanly.
+__global__ void __launch_bounds__(32, 1) wait_timeout_kernel(uint64_t limit_ns, uint32_t* status) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(ptx::smem_u32(&bar), 1);
+    abort_flag = 0u;
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+  const ptx::WaitCtx wait{&abort_flag, limit_ns};
+  const bool ok = ptx::mbar_wait(ptx::smem_u32(&bar), 0u, wait);
+  __syncwarp();
+  if (threadIdx.x == 0 && (!ok || abort_flag) && status != nullptr) atomicOr(status, 0x1u);
 }
 
 }  // namespace b200gmm

@@ -51,25 +51,51 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
-// Wait limit for every spin in the kernel.  A healthy wait lasts microseconds;
-// the limit only exists so that a logic error ends in an error status rather
-// than in a GPU that never comes back.
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Default wait limit for every spin in the kernels.  A healthy wait lasts
+// microseconds; the limit only exists so that a logic error ends in an error
+// status rather than in a GPU that never comes back.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 
+// What a waiting role needs to know: the limit and the CTA's abort flag.
+struct WaitCtx {
+  volatile uint32_t* abort_flag;
+  uint64_t limit_ns;
+};
+
 // Bounded wait on an mbarrier phase.  Returns false if the wait was abandoned,
-// either because this thread ran past kWaitLimitNs or because another thread of
-// the CTA already raised *abort_flag.  On a timeout the flag is raised so that
+// either because this thread ran past the limit or because another thread of
+// the CTA already raised the abort flag.  On a timeout the flag is raised so that
 // every other role of the CTA drains quickly too.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+//   kCluster  acquire at cluster scope: the data the arrival publishes was written
+//             by a thread of the other CTA of the pair;
+//   kBackoff  nanoseconds to sleep between polls (roles that wait for a whole
+//             tile's worth of MMAs and would otherwise burn issue slots).
+template <bool kCluster = false, int kBackoff = 0>
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w) {
+  auto poll = [&]() { return kCluster ? mbar_try_wait_cluster(bar, parity) : mbar_try_wait(bar, parity); };
+  if (poll()) return true;
   const uint64_t t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_flag = 1u;
+    if (poll()) return true;
+    if (kBackoff > 0) __nanosleep(kBackoff);
+    if ((it & 63u) == 0u || kBackoff > 0) {
+      if (*w.abort_flag) return false;
+      if (globaltimer_ns() - t0 > w.limit_ns) {
+        *w.abort_flag = 1u;
         return false;
       }
     }
@@ -214,6 +240,14 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
       : "r"(taddr)
       : "memory");
 }
+// 32 TMEM lanes x 8 consecutive fp32 columns -> 8 registers per thread.
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -243,6 +277,15 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
 // round trip per arrival.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+// The same arrival with release at cluster scope: it publishes ordinary stores the
+// arriving thread made to the other CTA's shared memory (st_shared_cluster_u32).
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
 // TMA loads issued by either CTA of a pair; the mbarrier operand is a

@@ -1,11 +1,12 @@
 // Tile schedule shared by the persistent kernel (device) and its host replay.
 //
 // The reference builds per-expert GEMM problems with a one-block kernel
-// (csrc/fill_arguments.cuh:34-98) and leaves the walk over tiles to CUTLASS'
-// device-only group scheduler.  Here both jobs are a few integers per CTA:
-// an exclusive prefix sum of batch_sizes (row_start), an exclusive prefix sum
-// of per-expert tile counts (tile_start), and a pure function from a global tile
-// index to (expert, rows, columns, k-range).
+// (csrc/fill_arguments.cuh:34-98), sorts them by k for wgrad (:80-86) and leaves
+// the walk over tiles to CUTLASS' device-only group scheduler.  Here all of it is
+// a few integers per CTA: an exclusive prefix sum of batch_sizes (row_start), an
+// order of the experts (perm), an exclusive prefix sum of per-expert tile counts
+// in that order (tile_start), and pure functions from a position in the launch
+// order to (expert, rows, columns, k-range).
 #pragma once
 
 #include <stdint.h>
@@ -28,6 +29,16 @@ constexpr int kBlockM = 128;  // output rows per CTA (UMMA M per CTA)
 constexpr int kBlockN = 256;  // output tile cols   (UMMA N)
 constexpr int kBlockK = 64;   // k depth per pipeline stage = one 128-byte swizzle row of bf16
 
+// Transposed ("swap-AB") tiles of the forward / dgrad layouts: the last rows of an
+// expert, when there are at most kLightRows of them, do not get a 128-row tile of
+// their own.  Instead 128 output COLUMNS ride the UMMA M dimension and the few
+// rows ride UMMA N (a multiple of 16), so a 5-row expert costs an N=16 instruction
+// instead of a padded 128 x 256 one.  Such a tile is kLightCols columns wide and
+// takes kLightK of the contraction per pipeline stage.
+constexpr int kLightRows = 64;
+constexpr int kLightCols = 128;
+constexpr int kLightK = 128;
+
 struct Problem {
   int mode;
   int z;
@@ -36,28 +47,52 @@ struct Problem {
   int64_t n;       // output columns
   int tile_m;      // output rows per scheduled tile: 128 (one CTA) or 256 (a CTA pair)
   int group_m;     // row-tiles swept together across the columns (L2 reuse of b)
-  int direct_store;  // 1: epilogue writes every row with plain stores (no TMA stores)
+  int light;       // 1: row remainders of <= kLightRows rows run as transposed tiles (NN/NT, tile_m 128)
+  int order;       // 0: experts in index order.  1: experts sorted by rows, largest first, and
+                   //    tiles taken alternately from the front and from the back of that order
+  int dynamic;     // 1: CTAs draw positions of the launch order from a global counter
+  int64_t wait_ns; // limit of every wait inside the kernel, in nanoseconds
 };
 
 struct Tile {
   int expert;
   int row0;        // NN/NT: first row of a/c (global); TN: first row of c[expert]
   int col0;        // first output column
-  int valid_rows;  // rows of this tile (of tile_m) that exist in the output
+  int valid_rows;  // rows of this tile that exist in the output
   int k_row0;      // TN: first contraction row in a/b (global); else 0
   int k_len;       // contraction length (k, or batch_sizes[expert] for TN)
+  int kind;        // 0: tile_m x 256 tile; 1: transposed tile (valid_rows <= kLightRows, kLightCols columns)
+  int stream;      // order == 1: 0 = taken from the front of the order, 1 = from the back
 };
 
 B200GMM_HD int ceil_div_i(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
 B200GMM_HD int col_tiles(const Problem& p) { return ceil_div_i(p.n, kBlockN); }
 
+// Row-tiles of tile_m rows an expert with `rows` rows gets, and the rows left over
+// for a transposed tile (0 if none).
+B200GMM_HD int heavy_row_tiles(const Problem& p, int64_t rows) {
+  if (!p.light) return ceil_div_i(rows, p.tile_m);
+  const int rem = static_cast<int>(rows % kBlockM);
+  return static_cast<int>(rows / kBlockM) + (rem > kLightRows ? 1 : 0);
+}
+B200GMM_HD int light_rows(const Problem& p, int64_t rows) {
+  if (!p.light) return 0;
+  const int rem = static_cast<int>(rows % kBlockM);
+  return rem <= kLightRows ? rem : 0;
+}
+
 // Tiles of one expert.  TN always has the full c[i] grid (empty experts still
 // need their zeros written, csrc/fill_arguments.cuh:100-119).
 B200GMM_HD int expert_tiles(const Problem& p, int64_t rows) {
   const int nt = col_tiles(p);
   if (p.mode == kTN) return ceil_div_i(p.d1, p.tile_m) * nt;
-  return ceil_div_i(rows, p.tile_m) * nt;
+  return heavy_row_tiles(p, rows) * nt + (light_rows(p, rows) > 0 ? ceil_div_i(p.n, kLightCols) : 0);
+}
+
+// Pipeline stages (ring slots) one tile consumes.
+B200GMM_HD int tile_stages(const Tile& t) {
+  return t.kind ? (t.k_len + kLightK - 1) / kLightK : (t.k_len + kBlockK - 1) / kBlockK;
 }
 
 // Within one expert: walk group_m row-tiles down, then step one column-tile
@@ -72,11 +107,13 @@ B200GMM_HD void decode_in_expert(int local, int row_tiles, int nt, int group_m, 
   *ni = r / gm;
 }
 
-// `local` = tile index relative to tile_start[expert]; rs/re = row_start[expert],
+// `local` = tile index relative to the expert's first tile; rs/re = row_start[expert],
 // row_start[expert+1] (already clamped to tokens).
 B200GMM_HD Tile make_tile(const Problem& p, int expert, int local, int rs, int re) {
   Tile t;
   t.expert = expert;
+  t.kind = 0;
+  t.stream = 0;
   const int nt = col_tiles(p);
   int mi, ni;
   if (p.mode == kTN) {
@@ -87,17 +124,37 @@ B200GMM_HD Tile make_tile(const Problem& p, int expert, int local, int rs, int r
     t.valid_rows = left < p.tile_m ? left : p.tile_m;
     t.k_row0 = rs;
     t.k_len = re - rs;
-  } else {
-    const int mt = ceil_div_i(re - rs, p.tile_m);
+    t.col0 = ni * kBlockN;
+    return t;
+  }
+  t.k_row0 = 0;
+  t.k_len = static_cast<int>(p.d1);
+  const int mt = heavy_row_tiles(p, re - rs);
+  if (local < mt * nt) {
     decode_in_expert(local, mt, nt, p.group_m, &mi, &ni);
     t.row0 = rs + mi * p.tile_m;
     const int left = re - t.row0;
     t.valid_rows = left < p.tile_m ? left : p.tile_m;
-    t.k_row0 = 0;
-    t.k_len = static_cast<int>(p.d1);
+    t.col0 = ni * kBlockN;
+  } else {
+    t.kind = 1;
+    t.row0 = rs + mt * kBlockM;
+    t.valid_rows = re - t.row0;
+    t.col0 = (local - mt * nt) * kLightCols;
   }
-  t.col0 = ni * kBlockN;
   return t;
+}
+
+// Position `t` of the launch order -> index into the sequence of all tiles laid
+// out expert after expert in `perm` order.  With order == 1 even positions walk
+// that sequence from the front (largest experts: long, tensor-bound tiles) and odd
+// positions from the back (smallest experts: short tiles bound by the weight or
+// output traffic), so both kinds are in flight at any time and the launch ends
+// on mid-sized tiles.
+B200GMM_HD int order_index(int order, int t, int total, int* stream) {
+  if (!order) { *stream = 0; return t; }
+  *stream = t & 1;
+  return (t & 1) ? total - 1 - (t >> 1) : (t >> 1);
 }
 
 // The nine per-expert values of the reference's GemmProblem

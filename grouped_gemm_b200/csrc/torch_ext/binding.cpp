@@ -68,12 +68,17 @@ void gmm(at::Tensor a, at::Tensor b, at::Tensor c, at::Tensor batch_sizes, bool 
     TORCH_CHECK(batch_sizes.is_contiguous(), "batch_sizes must be contiguous");
   } else {
     batch_sizes = batch_sizes.contiguous();
+    // The library copies host batch sizes to the device with an asynchronous copy.
+    // From pageable memory the data is staged before that call returns; from pinned
+    // memory the copy reads the caller's buffer later, on the stream, when the
+    // caller may already have changed or freed it.  Take a pageable copy.
+    if (batch_sizes.is_pinned()) batch_sizes = batch_sizes.clone();
   }
   TORCH_CHECK(z <= B200GMM_MAX_EXPERTS, b200gmm_strerror(B200GMM_ELIMIT));
 
-  // Note on the messages below: integers go in as std::to_string(...).  Streaming
-  // an int into a TORCH_CHECK message crashed inside the iostream number facets
-  // with this image's toolchain; strings are fine.
+  // Integers go into the messages below as std::to_string(...): streaming an int
+  // into a TORCH_CHECK message has been seen to crash inside the iostream number
+  // facets when libstdc++ versions are mixed; strings are always fine.
   c10::cuda::CUDAGuard guard(a.device());
   size_t ws_bytes = 0;
   int rc = b200gmm_workspace_bytes(static_cast<int>(z), &ws_bytes);

@@ -388,7 +388,8 @@ class PeerExchange:
         n = w.shape[1] if trans_b else w.shape[2]
         ws = torch.empty(self._ws_bytes, dtype=torch.uint8, device=self.device)
         rc = self._lib.b200gmm_run_scatter(
-            a.data_ptr(), w.data_ptr(), dest.data_ptr(), self.batch_sizes.data_ptr(), 1,
+            a.data_ptr(), w.data_ptr(), dest.data_ptr(), None, 0,   # addresses in peer buffers: table built here
+            self.batch_sizes.data_ptr(), 1,
             self.per_rank, a.shape[0], a.shape[1], n, 1 if trans_b else 0,
             ws.data_ptr(), self._ws_bytes, self._status.data_ptr(),
             torch.cuda.current_stream(self.device).cuda_stream)

@@ -41,6 +41,7 @@ extern "C" {
 #define B200GMM_STATUS_NEGATIVE_SIZE 0x2u  /* a batch size was < 0 (treated as 0) */
 #define B200GMM_STATUS_ROWS_OVERFLOW 0x4u  /* sum(batch_sizes) > rows of a (clamped) */
 #define B200GMM_STATUS_BAD_ROW_INDEX 0x8u  /* run_gather: a row index outside x (read as zeros) */
+#define B200GMM_STATUS_BAD_ROW_DEST 0x10u  /* a row_dest entry outside [dest_base, +dest_bytes) (row skipped) */
 
 /* Largest number of experts b200gmm_run_static accepts (its built-in scratch is
  * sized for this many). */
@@ -49,6 +50,11 @@ extern "C" {
 /* Number of int64 fields b200gmm_fill_offsets writes per expert:
  * m, n, k, lda, ldb, ldc, a_offset, b_offset, c_offset (offsets in elements). */
 #define B200GMM_FILL_FIELDS 9
+
+/* Number of fields b200gmm_schedule_host / b200gmm_schedule_device write per tile:
+ * expert, row0, col0, valid_rows, pipeline stages, kind (0: rows x 256 columns;
+ * 1: transposed tile of at most 64 rows x 128 columns). */
+#define B200GMM_SCHEDULE_FIELDS 6
 
 /*
  * Bytes of device scratch b200gmm_run needs for `z` experts (about 0.5 MB).
@@ -83,9 +89,10 @@ int b200gmm_workspace_bytes(int z, size_t* out_bytes);
  * sum(batch_sizes) are left untouched, as in the reference.
  *
  * batch_sizes may live in host memory (batch_sizes_on_device=0: it is copied
- * into the workspace with one cudaMemcpyAsync, so the host array must stay
- * valid until that copy has been issued, i.e. until this call returns when the
- * host array is pageable) or in device memory (=1: never read by the host, no
+ * into the workspace with one cudaMemcpyAsync.  A pageable array is staged
+ * before this call returns and may be reused at once; a PINNED array is read
+ * later, when the stream reaches the copy, and must stay valid and unchanged
+ * until then) or in device memory (=1: never read by the host, no
  * synchronisation).
  *
  * `workspace` is device memory of at least b200gmm_workspace_bytes(z) bytes,
@@ -109,7 +116,8 @@ int b200gmm_run(const void* a, const void* b, void* c,
  * Who needs it: code that runs where allocating is not an option -- an inference
  * server that has already given all free HBM to its own cache pool, a plugin
  * that is handed input and output buffers and nothing else, a latency-critical
- * thread that must not take the allocator's or the driver's locks.  The scratch
+ * thread that must not take the allocator's locks (after the first call on a
+ * device this function takes no lock of its own either).  The scratch
  * (device copy of batch_sizes, per-CTA tensor-map copies) lives in a fixed
  * array inside the library image, about 0.5 MB, present on every GPU that loads
  * the library for as long as the process runs.  This function calls no
@@ -144,10 +152,20 @@ int b200gmm_run_static(const void* a, const void* b, void* c,
  * over the output is needed.  Remote memory is only written.  The caller orders
  * the kernel against the readers on the other GPUs (a barrier after it).  Rows
  * past sum(batch_sizes) are not written.  Other arguments as in b200gmm_run.
+ *
+ * `dest_base` / `dest_bytes` declare the one buffer all destinations lie in: a
+ * row whose address is below dest_base, whose n elements would end past
+ * dest_base + dest_bytes, or whose address is not 16-byte aligned is NOT written
+ * and B200GMM_STATUS_BAD_ROW_DEST is raised.  Pass the output tensor here
+ * whenever the table was computed from indices of unknown provenance.  NULL / 0
+ * switches the check off for callers that built the table themselves, e.g. from
+ * rows of several peer buffers.  The same pair, with the same meaning, follows
+ * row_dest in b200gmm_run_combine, b200gmm_run_gather and b200gmm_run_swiglu.
  * The reference has no counterpart (single GPU; its callers un-sort the output
  * themselves).
  */
 int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
+                        const void* dest_base, int64_t dest_bytes,
                         const int64_t* batch_sizes, int batch_sizes_on_device,
                         int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
                         void* workspace, size_t workspace_bytes,
@@ -168,6 +186,7 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
  * un-sort, weight and sum in kernels of their own.
  */
 int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest,
+                        const void* dest_base, int64_t dest_bytes,
                         const float* row_weight, int accumulate,
                         const int64_t* batch_sizes, int batch_sizes_on_device, int z,
                         int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
@@ -192,6 +211,7 @@ int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest,
  */
 int b200gmm_run_gather(const void* x, int64_t x_rows, const int32_t* row_index,
                        const void* b, void* c, const int64_t* row_dest,
+                       const void* dest_base, int64_t dest_bytes,
                        const int64_t* batch_sizes, int batch_sizes_on_device,
                        int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
                        void* workspace, size_t workspace_bytes,
@@ -229,7 +249,8 @@ int b200gmm_run_gather_wgrad(const void* x, int64_t x_rows, const int32_t* row_i
  * concatenated weights) and apply the activation in a separate kernel.
  */
 int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void* c,
-                       const int64_t* row_dest, const int64_t* batch_sizes,
+                       const int64_t* row_dest, const void* dest_base, int64_t dest_bytes,
+                       const int64_t* batch_sizes,
                        int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1,
                        int64_t n, int trans_b, void* workspace, size_t workspace_bytes,
                        uint32_t* device_status, void* cuda_stream);
@@ -255,8 +276,8 @@ int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items,
 
 /*
  * Device-side argument fill on its own, for inspection and bit-exact tests:
- * runs the same warp-scan the GEMM kernel runs in its prologue and writes
- * z x B200GMM_FILL_FIELDS int64 values (expert-major) to `out_device`.
+ * runs the same warp-scan step the GEMM kernels build their schedule from and
+ * writes z x B200GMM_FILL_FIELDS int64 values (expert-major) to `out_device`.
  * Semantics of each field follow FillArguments (csrc/fill_arguments.cuh:59-78)
  * and its host twin MakeArgumentsOnHost (csrc/grouped_gemm.cu:160-175),
  * evaluated in int64.  `batch_sizes_device` must be device memory.
@@ -267,9 +288,14 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z,
 
 /*
  * Host replay of the tile schedule the persistent kernel walks (same
- * __host__ __device__ code as the kernel).  Writes, for every tile index in
- * launch order, {expert, row0, col0, valid_rows, k_blocks} as int64 into `out`
- * (5 per tile, at most `max_tiles` tiles) and the tile count into *n_tiles.
+ * __host__ __device__ code as the kernel).  Writes, for every position of the
+ * launch order, B200GMM_SCHEDULE_FIELDS int64 values into `out` (at most
+ * `max_tiles` tiles) and the tile count into *n_tiles.  CTAs draw positions
+ * from a global counter in this order; where tile durations differ widely
+ * (trans_a, and the one-CTA variant) the experts are first sorted by their
+ * number of rows, largest first (the reference sorts its wgrad problems the
+ * same way, csrc/fill_arguments.cuh:80-86), and positions alternate between
+ * the front and the back of that order.
  * `cluster_ctas` selects the kernel variant: 1 (each CTA owns 128-row tiles),
  * 2 (a pair of CTAs owns 256-row tiles) or 0 (whatever b200gmm_run would pick
  * for these shapes).  Pure host arithmetic; needs no GPU.  It has no
@@ -280,6 +306,34 @@ int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z,
                           int64_t tokens, int64_t dim_a1, int64_t n,
                           int trans_a, int trans_b, int cluster_ctas,
                           int64_t* out, int64_t max_tiles, int64_t* n_tiles);
+
+/*
+ * The same schedule as the GPU builds it: one CTA runs the GEMM kernels' own
+ * prologue (prefix sums of batch_sizes, expert order, tile prefix sums) and
+ * tile decoder and writes B200GMM_SCHEDULE_FIELDS int32 values per tile into
+ * `out_device` (at most `max_tiles` tiles) and the tile count into
+ * *n_tiles_device.  For tests: the result must equal b200gmm_schedule_host's
+ * exactly.  Replaces nothing in the reference (its tests never look at the
+ * argument arrays FillArguments writes, csrc/fill_arguments.cuh:88-97).
+ */
+int b200gmm_schedule_device(const int64_t* batch_sizes_device, int z,
+                            int64_t tokens, int64_t dim_a1, int64_t n,
+                            int trans_a, int trans_b, int cluster_ctas,
+                            int32_t* out_device, int64_t max_tiles,
+                            int32_t* n_tiles_device, uint32_t* device_status,
+                            void* cuda_stream);
+
+/*
+ * Exercises the kernels' bounded wait in isolation: one warp waits on an
+ * mbarrier that nothing signals, gives up after `limit_ns` nanoseconds (at most
+ * 100 ms) and ORs B200GMM_STATUS_TIMEOUT into *device_status, which is how every
+ * wait inside the GEMM kernels ends if its partner never arrives (their limit is
+ * 2 s, or B200GMM_WAIT_LIMIT_NS nanoseconds from the environment).  No copy or
+ * MMA is in flight, nothing faults, the context stays usable.  The reference has
+ * no counterpart (its kernels have no waits of their own).
+ */
+int b200gmm_selftest_wait_timeout(int64_t limit_ns, uint32_t* device_status,
+                                  void* cuda_stream);
 
 /* Tile shape of a kernel variant (cluster_ctas = 1 or 2): out[0]=rows,
  * out[1]=cols, out[2]=k depth per pipeline stage. */

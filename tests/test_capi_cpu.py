@@ -77,22 +77,24 @@ def test_fused_entry_points_reject_bad_arguments_before_cuda():
     bs = np.array([64, 64], dtype=np.int64)
     dummy = np.zeros(64, dtype=np.int64).ctypes.data  # any non-null, 16-byte aligned address
     # scatter and combine need a destination table
-    assert lib.b200gmm_run_scatter(dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_combine(dummy, dummy, None, None, 1, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_scatter(dummy, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_combine(dummy, dummy, None, None, 0, None, 1, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
     # combine: weights must be 4-byte aligned; k == 0 overwrite has nothing to write through
-    assert lib.b200gmm_run_combine(dummy, dummy, dummy, dummy + 2, 1, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -2
-    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 0, bs.ctypes.data, 0, 2, 128, 0, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 1, bs.ctypes.data, 0, 2, 128, 0, 64, 0, None, 0, None, None) == 0
+    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 0, dummy + 2, 1, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -2
+    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 0, None, 0, bs.ctypes.data, 0, 2, 128, 0, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_combine(dummy, dummy, dummy, None, 0, None, 1, bs.ctypes.data, 0, 2, 128, 0, 64, 0, None, 0, None, None) == 0
     # gather: row index table, a non-empty source below 2^31 rows, an output of some kind
-    assert lib.b200gmm_run_gather(dummy, 100, None, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_gather(dummy, 0, dummy, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_gather(dummy, 2 ** 31, dummy, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_gather(dummy, 100, dummy, dummy, None, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 100, None, dummy, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 0, dummy, dummy, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 2 ** 31, dummy, dummy, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_gather(dummy, 100, dummy, dummy, None, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
     # swiglu: both weight tensors, an output, column count a multiple of 8
-    assert lib.b200gmm_run_swiglu(dummy, dummy, None, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy, None, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
-    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 60, 0, None, 0, None, None) == -2
-    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy + 8, dummy, None, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -2
+    assert lib.b200gmm_run_swiglu(dummy, dummy, None, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy, None, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
+    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 60, 0, None, 0, None, None) == -2
+    assert lib.b200gmm_run_swiglu(dummy, dummy, dummy + 8, dummy, None, None, 0, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -2
+    # a destination window needs a destination table
+    assert lib.b200gmm_run_gather(dummy, 100, dummy, dummy, dummy, None, dummy, 64, bs.ctypes.data, 0, 2, 128, 64, 64, 0, None, 0, None, None) == -1
     # the static-scratch entry point refuses more experts than its scratch holds
     assert lib.b200gmm_run_static(dummy, dummy, dummy, bs.ctypes.data, 0, 257, 128, 64, 64, 0, 0, None, None) == -3
 
@@ -105,7 +107,7 @@ def _schedule(sizes, tokens, d1, n, trans_a, trans_b, ctas=1):
     rc = lib.b200gmm_schedule_host(ptr, len(sizes), tokens, d1, n, trans_a, trans_b, ctas, None, 0,
                                    ctypes.byref(count))
     assert rc == 0
-    out = np.zeros((count.value, 5), dtype=np.int64)
+    out = np.zeros((count.value, _capi.SCHEDULE_FIELDS), dtype=np.int64)
     rc = lib.b200gmm_schedule_host(ptr, len(sizes), tokens, d1, n, trans_a, trans_b, ctas,
                                    out.ctypes.data, count.value, ctypes.byref(count))
     assert rc == 0
@@ -119,6 +121,7 @@ SIZE_SETS = [
     [1],
     [3400, 1030, 17412, 1225, 363, 5908, 1691, 1739],
     [7, 0, 300, 129, 128, 127, 0, 1025],
+    [64, 65, 192, 193, 16, 17],
 ]
 
 
@@ -127,19 +130,26 @@ SIZE_SETS = [
 @pytest.mark.parametrize("n", [128, 256, 328, 1536])
 @pytest.mark.parametrize("ctas", [1, 2])
 def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n, ctas):
+    """Every output element belongs to exactly one tile: 128-column granularity,
+    since the transposed tiles of the one-CTA variant are 128 columns wide."""
     tokens = sum(sizes)
     tile_m = 128 * ctas
     tiles = _schedule(sizes, tokens, 512, n, 0, trans_b, ctas)
-    cover = np.zeros((tokens, (n + 255) // 256), dtype=np.int32)
+    cover = np.zeros((tokens, (n + 127) // 128), dtype=np.int32)
     starts = np.concatenate([[0], np.cumsum(sizes)])
-    for e, row0, col0, valid, kblocks in tiles:
-        assert 0 < valid <= tile_m and col0 % 256 == 0 and col0 < n
+    for e, row0, col0, valid, stages, kind in tiles:
+        width = 128 if kind else 256
+        assert col0 % width == 0 and col0 < n
         assert starts[e] <= row0 and row0 + valid <= starts[e + 1], "tile leaves its expert's rows"
-        assert kblocks == 512 // 64
-        cover[row0:row0 + valid, col0 // 256] += 1
+        if kind:
+            assert ctas == 1 and 0 < valid <= 64 and stages == 512 // 128
+            assert row0 + valid == starts[e + 1], "a transposed tile holds an expert's last rows"
+        else:
+            assert 0 < valid <= tile_m and stages == 512 // 64
+            if ctas == 1:
+                assert valid > 64, "row remainders of at most 64 rows go to transposed tiles"
+        cover[row0:row0 + valid, col0 // 128:(col0 + width + 127) // 128] += 1
     assert (cover == 1).all()
-    # experts appear in order (the kernel's forward-only expert cursor relies on it)
-    assert (np.diff(tiles[:, 0]) >= 0).all() if len(tiles) else True
 
 
 @pytest.mark.parametrize("sizes", SIZE_SETS)
@@ -153,11 +163,27 @@ def test_schedule_wgrad_full_grid_for_every_expert(sizes, ctas):
     for e, size in enumerate(sizes):
         mine = tiles[tiles[:, 0] == e]
         cover = np.zeros(((m + tile_m - 1) // tile_m, (n + 255) // 256), dtype=np.int32)
-        for _, row0, col0, valid, kblocks in mine:
+        for _, row0, col0, valid, stages, kind in mine:
+            assert kind == 0
             assert valid == min(tile_m, m - row0)
-            assert kblocks == (size + 63) // 64  # 0 for an empty expert: zero-fill tile
+            assert stages == (size + 63) // 64  # 0 for an empty expert: zero-fill tile
             cover[row0 // tile_m, col0 // 256] += 1
         assert (cover == 1).all()
+
+
+def test_schedule_order_largest_and_smallest_experts_alternate():
+    """wgrad launch order: experts sorted by rows, largest first; even positions
+    walk that order from the front, odd positions from the back, so the order
+    ends on the mid-sized experts."""
+    sizes = [10, 500, 0, 70, 3000, 200]
+    tiles = _schedule(sizes, sum(sizes), 128, 256, 1, 0, 1)     # one tile per expert
+    assert tiles[:, 0].tolist() == [4, 2, 1, 0, 5, 3]
+    # equal sizes keep their index order (stable), whichever end they are taken from
+    tiles = _schedule([64, 64, 64, 64], 256, 128, 256, 1, 0, 1)
+    assert tiles[:, 0].tolist() == [0, 3, 1, 2]
+    # the pair variant of the forward layouts keeps the experts in index order
+    tiles = _schedule([600, 100, 900], 1600, 128, 256, 0, 0, 2)
+    assert (np.diff(tiles[:, 0]) >= 0).all()
 
 
 def test_schedule_clamps_rows_past_tokens():
@@ -173,3 +199,4 @@ def test_variant_choice_depends_on_shapes_only():
     big = _schedule([4096] * 8, 32768, 512, 512, 0, 0, 0)
     small = _schedule([64] * 64, 4096, 512, 512, 0, 0, 0)
     assert int(big[:, 3].max()) == 256 and int(small[:, 3].max()) == 64
+    assert (small[:, 5] == 1).all(), "64-row experts run as transposed tiles"

@@ -1,0 +1,113 @@
+"""The drop-in by name: code written against tgale96/grouped_gemm does
+``import grouped_gemm`` (grouped_gemm/__init__.py:1-2 there) and the package
+itself does ``import grouped_gemm_backend`` (backend.py:8 there).  Both names
+must exist here and lead to the B200 implementation.
+
+The last test runs the reference's own test file, unmodified, over this backend
+when GROUPED_GEMM_REFERENCE points at a checkout of the reference.
+"""
+import importlib.util
+import os
+import subprocess
+import sys
+import unittest
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_names_resolve_to_this_library():
+    import grouped_gemm
+    import grouped_gemm_backend
+    import grouped_gemm_b200
+    assert grouped_gemm.ops.gmm is grouped_gemm_b200.ops.gmm
+    assert grouped_gemm.backend.gmm is grouped_gemm_b200.backend.gmm
+    # as in the reference: ops.backend is the Python backend module, whose own
+    # ``backend`` attribute is the compiled module
+    assert grouped_gemm.ops.backend is grouped_gemm.backend
+    assert grouped_gemm.backend.backend is grouped_gemm_backend
+    assert callable(grouped_gemm_backend.gmm)
+    assert os.path.dirname(os.path.abspath(grouped_gemm_backend.__file__)) == ROOT
+
+
+def test_compiled_module_checks_like_the_reference():
+    """grouped_gemm_backend.gmm(a, b, c, batch_sizes, trans_a, trans_b): positional,
+    returns None, RuntimeError on what the reference's TORCH_CHECKs refuse
+    (csrc/grouped_gemm.cu:476-540).  No GPU needed to be refused."""
+    import grouped_gemm_backend
+    a = torch.zeros(8, 16, dtype=torch.bfloat16)
+    b = torch.zeros(2, 16, 24, dtype=torch.bfloat16)
+    c = torch.zeros(8, 24, dtype=torch.bfloat16)
+    bs = torch.tensor([4, 4])
+    with pytest.raises(RuntimeError):
+        grouped_gemm_backend.gmm(a, b, c, bs, True, True)     # both transposes
+    with pytest.raises(RuntimeError):
+        grouped_gemm_backend.gmm(a, b, c, bs, False, False)   # CPU tensors
+
+
+@pytest.mark.gpu
+def test_import_grouped_gemm_and_run():
+    import grouped_gemm
+    a = torch.ones(192, 128, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    b = torch.ones(3, 128, 64, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+    bs = torch.tensor([64, 0, 128])
+    out = grouped_gemm.ops.gmm(a, b, bs)
+    assert bool((out == 128).all())
+    out.sum().backward()
+    assert bool((a.grad == 64).all())
+    assert bool((b.grad[0] == 64).all()) and bool((b.grad[1] == 0).all()) and bool((b.grad[2] == 128).all())
+    # the reference's direct backend call with a caller-provided c (ops_test.py:143-158)
+    c = torch.ones(3, 128, 64, device="cuda", dtype=torch.bfloat16)
+    got = grouped_gemm.ops.backend.gmm(a.detach(), torch.ones(192, 64, device="cuda", dtype=torch.bfloat16), bs,
+                                       trans_a=True, c=c)
+    assert got is c and bool((c[1] == 0).all()) and bool((c[2] == 128).all())
+
+
+@pytest.mark.gpu
+def test_reference_ops_test_runs_unmodified_over_this_backend():
+    """GROUPED_GEMM_REFERENCE=<checkout of tgale96/grouped_gemm>: load its
+    grouped_gemm/ops_test.py as it is (it imports ``grouped_gemm.ops``, which is
+    this library) and run all of its cases (ops_test.py:56-158)."""
+    ref = os.environ.get("GROUPED_GEMM_REFERENCE")
+    if not ref:
+        pytest.skip("GROUPED_GEMM_REFERENCE not set")
+    path = os.path.join(ref, "grouped_gemm", "ops_test.py")
+    if not os.path.exists(path):
+        pytest.skip(f"{path} not found")
+    pytest.importorskip("absl.testing.parameterized")
+    spec = importlib.util.spec_from_file_location("reference_ops_test", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    import grouped_gemm_b200
+    assert module.ops.gmm is grouped_gemm_b200.ops.gmm, "the reference's tests must be driving this library"
+    suite = unittest.defaultTestLoader.loadTestsFromModule(module)
+    assert suite.countTestCases() >= 52
+    result = unittest.TextTestRunner(verbosity=0).run(suite)
+    assert result.wasSuccessful(), f"{len(result.failures)} failures, {len(result.errors)} errors"
+    assert result.testsRun >= 52
+
+
+def test_pip_install_gives_the_reference_names(tmp_path):
+    """``pip install --target`` of this tree yields importable ``grouped_gemm``,
+    ``grouped_gemm_backend`` and ``grouped_gemm_b200`` (reference setup.py:33-48)."""
+    target = tmp_path / "site"
+    cmd = [sys.executable, "-m", "pip", "install", "--no-index", "--no-deps", "--no-build-isolation", "--quiet",
+           "--target", str(target), ROOT]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    if res.returncode != 0 and "No module named pip" in res.stderr:
+        pytest.skip("pip is not available")
+    assert res.returncode == 0, res.stderr[-2000:]
+    for name in ("grouped_gemm", "grouped_gemm_b200"):
+        assert (target / name / "__init__.py").exists()
+    assert (target / "grouped_gemm_backend.so").exists()
+    assert (target / "grouped_gemm_b200" / "csrc" / "libb200gmm.so").exists()
+    probe = ("import grouped_gemm, grouped_gemm_backend, os; "
+             "assert grouped_gemm.backend.backend is grouped_gemm_backend; "
+             f"assert os.path.dirname(grouped_gemm.__file__).startswith({str(target)!r}); "
+             f"assert grouped_gemm_backend.__file__.startswith({str(target)!r}); print('ok')")
+    env = dict(os.environ, PYTHONPATH=str(target))
+    res = subprocess.run([sys.executable, "-c", probe], capture_output=True, text=True, cwd=str(tmp_path), env=env,
+                         timeout=600)
+    assert res.returncode == 0 and "ok" in res.stdout, res.stderr[-2000:]

@@ -717,3 +717,41 @@ def test_status_flags_bad_batch_sizes(gg):
     assert gg.backend.device_status() & 0x4
     assert bool((c[100:] == 0).all())
     word.zero_()
+
+
+@pytest.mark.parametrize("accumulate", [False, True])
+@pytest.mark.parametrize("sizes", [[70, 130], [600, 40, 0, 9]])
+def test_gmm_scatter_row_index_out_of_range_is_skipped_and_flagged(gg, sizes, accumulate):
+    """A destination index outside ``out`` is never written through (neither by
+    the store nor by the reduce-add form): the row is dropped, the words around
+    ``out`` stay as they were and the status word says so.  The same index then
+    reaches the kernel again through the backward of the gathered product."""
+    torch.manual_seed(21)
+    T, k, n, R = sum(sizes), 128, 264, 37
+    a = torch.randn(T, k, device="cuda").bfloat16()
+    b = torch.randn(len(sizes), k, n, device="cuda").bfloat16() * 0.1
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    idx = torch.randperm(T, device="cuda") % R if accumulate else torch.randperm(max(T, R), device="cuda")[:T] % max(T, R)
+    rows = R if accumulate else max(T, R)
+    # ``out`` sits inside a larger buffer whose margins must survive
+    margin = 16
+    buf = torch.full((rows + 2 * margin, n), 7.0, device="cuda", dtype=torch.bfloat16)
+    out = buf[margin:margin + rows]
+    out.zero_()
+    word = gg.backend.backend.device_status("cuda")
+    good = torch.zeros_like(out)
+    gg.backend.gmm_scatter(a, b, bs, good, idx, accumulate=accumulate)
+    assert gg.backend.device_status() == 0
+    bad_rows = torch.tensor([1, T // 2, T - 1], device="cuda")
+    idx_bad = idx.clone()
+    idx_bad[bad_rows] = torch.tensor([-1, rows, rows + 5], device="cuda")   # just below, just past, inside the margin
+    gg.backend.gmm_scatter(a, b, bs, out, idx_bad, accumulate=accumulate)
+    assert gg.backend.device_status() & 0x10
+    word.zero_()
+    assert bool((buf[:margin] == 7.0).all()) and bool((buf[margin + rows:] == 7.0).all()), "wrote outside out"
+    if not accumulate:
+        # every row but the three dropped ones arrived
+        keep = torch.ones(T, dtype=torch.bool, device="cuda")
+        keep[bad_rows] = False
+        assert torch.equal(out[idx[keep]], good[idx[keep]])
+        assert bool((out[idx[bad_rows]] == 0).all())

@@ -12,6 +12,7 @@ import pytest
 import torch
 
 from grouped_gemm_b200 import _capi
+from oracle import gmm_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -57,6 +58,9 @@ def test_static_entry_matches_workspace_entry_on_two_calls_in_a_row():
         (1, [300, 0, 77, 515, 64], 384, 520, "tn", True),
         (2, [129, 1000, 5, 0, 2000, 31], 512, 768, "nn", False),
         (3, [700, 45], 256, 264, "nt", True),
+        # wgrad with batch_sizes in host memory: copies them into the scratch and
+        # edits the tensor maps that live behind them
+        (4, [5, 130, 0, 64], 256, 264, "tn", False),
     ]
     for seed, sizes, d1, n, mode, on_device in calls:
         a, b, shape = _problem(seed, sizes, d1, n, mode)
@@ -89,3 +93,37 @@ def test_static_entry_rejects_too_many_experts():
     assert _run("workspace", a, b, c, bs, False, False, status) == 0
     torch.cuda.synchronize()
     assert bool((c == 0).all())
+
+
+@pytest.mark.parametrize("mode,on_device", [("nn", False), ("tn", True), ("tn", False)])
+def test_static_entry_at_its_expert_limit_against_the_oracle(mode, on_device):
+    """z = 256, the most the built-in scratch holds: the batch_sizes copy and the
+    tensor-map copies sit back to back in it, so this is where their sizes would
+    collide if either drifted.  Checked against the CPU oracle, not against the
+    other entry point."""
+    z = _capi.STATIC_MAX_EXPERTS
+    g = torch.Generator().manual_seed(7)
+    sizes = [int(v) for v in torch.randint(0, 40, (z,), generator=g)]
+    sizes[3], sizes[100], sizes[255] = 0, 300, 129
+    d1, n = 128, 264
+    T = sum(sizes)
+    a_cpu = torch.randn(T, d1, generator=g).bfloat16()
+    bs_cpu = torch.tensor(sizes, dtype=torch.int64)
+    if mode == "tn":
+        b_cpu = torch.randn(T, n, generator=g).bfloat16()
+        want = gmm_oracle.gmm(a_cpu, b_cpu, bs_cpu, trans_a=True)
+        shape = (z, d1, n)
+    else:
+        b_cpu = (torch.randn(z, d1, n, generator=g) * 0.1).bfloat16()
+        want = gmm_oracle.gmm(a_cpu, b_cpu, bs_cpu)
+        shape = (T, n)
+    a, b = a_cpu.cuda(), b_cpu.cuda()
+    bs = bs_cpu.cuda() if on_device else bs_cpu
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = torch.full(shape, 3.0, dtype=torch.bfloat16, device="cuda")
+    for _ in range(2):  # twice: the second call finds the first one's scratch
+        assert _run("static", a, b, got, bs, mode == "tn", False, status) == 0
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    err = (got.float().cpu() - want.float()).abs()
+    assert bool((err <= ATOL + RTOL * want.float().abs()).all()), float(err.max())
