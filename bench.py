@@ -448,7 +448,7 @@ def run_single(args):
     if args.fused:
         del a, b, grad
         fused = fused_neighbours(backend, dev, bs)
-    scaling_base = ep_value_single(args.steps, dev) if args.scaling_base else None
+    scaling_base = None if args.no_scaling_base else ep_value_single(args.steps, dev)
     baseline = cpu_baseline() if not args.no_cpu_baseline else None
 
     line = {
@@ -722,8 +722,9 @@ def ep_flops():
 
 
 def ep_value_single(steps, dev):
-    """Config 5 on one GPU (all 64 experts local, rows only permuted): the
-    denominator for strong-scaling efficiency of the multi-GPU lines."""
+    """The multi-GPU workload on one GPU (all 64 experts local, rows only
+    permuted), timed with the step function the multi-GPU lines use: the
+    denominator for their strong-scaling efficiency."""
     from grouped_gemm_b200 import backend, expert_parallel as ep
     ids = ep_routing(EP["tokens"], EP["z"], EP["top_k"]).to(dev)
     g = torch.Generator(device=dev).manual_seed(100)
@@ -732,16 +733,58 @@ def ep_value_single(steps, dev):
     grad = torch.randn(EP["tokens"] * EP["top_k"], EP["ffn"], device=dev, generator=g).bfloat16()
     px = ep.PeerExchange(ids, EP["z"], EP["hidden"], EP["ffn"], single_rank=True)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
-    step = lambda: px.step(x, w, grad, gmm_fn)
-    for _ in range(2):
+    step = lambda: px.step_fused(x, w, grad, gmm_fn, x_next=x)
+    for _ in range(3):
         step()
-    steps = max(2, min(steps, 5))
+    steps = max(steps, 2)
     ms = time_loop(step, steps)
     out = {"workload": workload_config(2)["workload"].replace("over 2 ranks", "over 1 rank"),
-           "value": ep_flops() / ms / 1e9, "unit": UNIT, "ms_per_step": ms, "steps": steps}
+           "value": ep_flops() / ms / 1e9, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+           "step": "PeerExchange.step_fused, as in the multi-GPU lines"}
     del x, w, grad, px
     torch.cuda.empty_cache()
     return out
+
+
+def ep_parity(ep, px, plan, x, w, grad, gmm_fn, backend, rank):
+    """Before anything is timed: one step over peer memory against the same step
+    over NCCL all-to-all (bit for bit, every element of out_rows, dx, dw), and the
+    local GEMMs of this rank against an fp32 CPU product on sampled rows."""
+    want = ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+    got = px.step_fused(x, w, grad, gmm_fn, x_next=x)
+    got = [t.clone() for t in got]
+    got2 = px.step_fused(x, w, grad, gmm_fn, x_next=x)     # the step that found its rows dispatched ahead
+    torch.cuda.synchronize()
+    same = all(torch.equal(u, v) for u, v in zip(got, want)) and all(torch.equal(u, v) for u, v in zip(got2, want))
+    # local GEMMs vs fp32 on the host: 64 rows of the forward and of dgrad, 8 rows of one expert's wgrad
+    a = ep.dispatch(x, plan)
+    gl = ep.dispatch_rows(grad, plan)
+    sizes = plan.batch_sizes_host
+    starts = np.concatenate([[0], np.cumsum(sizes)])
+    rng = np.random.default_rng(7 + rank)
+    rows = np.sort(rng.choice(int(starts[-1]), size=min(64, int(starts[-1])), replace=False))
+    expert_of = np.searchsorted(starts, rows, side="right") - 1
+    c = backend.gmm(a, w, plan.batch_sizes)
+    da = backend.gmm(gl, w, plan.batch_sizes, trans_b=True)
+    dw = backend.gmm(a, gl, plan.batch_sizes, trans_a=True)
+    max_err = 0.0
+    ok = True
+    for e in np.unique(expert_of):
+        sel = torch.from_numpy(rows[expert_of == e]).to(a.device)
+        we = w[int(e)].float().cpu()
+        for got_rows, ref in ((c[sel], a[sel].float().cpu() @ we), (da[sel], gl[sel].float().cpu() @ we.t())):
+            err = (got_rows.float().cpu() - ref).abs()
+            max_err = max(max_err, float(err.max()))
+            ok = ok and bool((err <= 1e-2 + 1e-2 * ref.abs()).all())
+    e0 = int(np.argmax(sizes))
+    sl = slice(int(starts[e0]), int(starts[e0 + 1]))
+    krows = torch.from_numpy(rng.choice(EP["hidden"], size=8, replace=False)).to(a.device)
+    ref = a[sl][:, krows].float().cpu().t() @ gl[sl].float().cpu()
+    err = (dw[e0][krows].float().cpu() - ref).abs()
+    max_err = max(max_err, float(err.max()))
+    ok = ok and bool((err <= 1e-2 * float(ref.abs().max()) + 1e-2 * ref.abs()).all())
+    return {"checked": True, "peer_path_equals_nccl_path_bitwise": bool(same), "local_gemms_within_tolerance": bool(ok),
+            "max_abs_err_vs_fp32": max_err, "rows_sampled": int(len(rows))}
 
 
 class StdoutToStderr:
@@ -799,13 +842,17 @@ def measure_multi(args):
             px = None
             args.exchange = "nccl"
             exchange_note = exchange_note or " (peer-memory setup failed on another rank, NCCL exchange used instead)"
+    parity = None
     if px is not None:
-        if args.overlap:
-            step = lambda: px.step_overlapped(x, w, grad, gmm_fn)
-        elif args.no_fused_combine:
+        if not args.no_parity:
+            parity = ep_parity(ep, px, plan, x, w, grad, gmm_fn, backend, rank)
+        if args.no_fused_combine:
             step = lambda: px.step(x, w, grad, gmm_fn)
+        elif args.no_overlap:
+            step = lambda: px.step_fused(x, w, grad, gmm_fn, overlap=False)
         else:
-            step = lambda: px.step_fused(x, w, grad, gmm_fn)
+            # x_next: the next step's activations are dispatched under this step's wgrad
+            step = lambda: px.step_fused(x, w, grad, gmm_fn, x_next=x)
         exchange_step = step
     else:
         step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
@@ -813,11 +860,24 @@ def measure_multi(args):
     for _ in range(max(args.warmup, 3)):
         step()
     launches0 = _capi.launch_count()
+    round_ms = []
     with ClockSampler(local) as clocks:
-        ms_total = timed_region(step, args.steps, world)
-    launches = (_capi.launch_count() - launches0) * world
-    ms_step = ms_total / args.steps
+        for _ in range(args.rounds):
+            round_ms.append(timed_region(step, args.steps, world) / args.steps)
+    launches = (_capi.launch_count() - launches0) * world // args.rounds
+    ms_step = sorted(round_ms)[len(round_ms) // 2]
     value = ep_flops() / ms_step / 1e9
+
+    # the same step with NCCL all-to-all as the exchange (the baseline of this path)
+    nccl_exchange = None
+    if px is not None and not args.no_nccl_compare:
+        nccl_step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
+        for _ in range(2):
+            nccl_step()
+        n_steps = max(2, min(args.steps, 5))
+        ms_nccl = timed_region(nccl_step, n_steps, world) / n_steps
+        nccl_exchange = {"value": ep_flops() / ms_nccl / 1e9, "unit": UNIT, "ms_per_step": ms_nccl, "steps": n_steps}
+        torch.cuda.empty_cache()
 
     # split: local GEMMs alone (max over ranks), to show the exchange share
     a = ep.dispatch(x, plan)
@@ -853,6 +913,17 @@ def measure_multi(args):
     peaks = measured_peaks()
     status = torch.tensor([backend.device_status(dev)], device=dev)
     dist.all_reduce(status, op=dist.ReduceOp.MAX)
+    if parity is not None:
+        # a rank that disagrees makes the whole line disagree
+        flags = torch.tensor([0 if parity["peer_path_equals_nccl_path_bitwise"] else 1,
+                              0 if parity["local_gemms_within_tolerance"] else 1], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MAX)
+        err = torch.tensor([parity["max_abs_err_vs_fp32"]], device=dev)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        parity["peer_path_equals_nccl_path_bitwise"] = not bool(flags[0].item())
+        parity["local_gemms_within_tolerance"] = not bool(flags[1].item())
+        parity["max_abs_err_vs_fp32"] = float(err.item())
+        parity["ranks"] = world
     line = None
     if rank == 0:
         line = {
@@ -865,11 +936,15 @@ def measure_multi(args):
                          "unit": "TFLOP/s", "frac": ep_flops() / world / ms_gemm / 1e9 / peaks["sustained"],
                          "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (per GPU)", "traffic": None},
             "exchange": (("peer memory over NVLink (symmetric memory): "
-                          + ("4 row pushes per step" if (args.no_fused_combine or args.overlap) else
+                          + ("4 row pushes per step" if args.no_fused_combine else
                              "2 row pushes (dispatch) per step, both combines written by the GEMM epilogues "
                              "straight into the token owners' buffers")
-                          + (", on a second stream under the GEMMs" if args.overlap else ""))
+                          + ("" if (args.no_fused_combine or args.no_overlap) else
+                             "; the gradient dispatch runs under the forward GEMM and the next step's activation "
+                             "dispatch under this step's wgrad GEMM, on a second stream"))
                          if args.exchange == "peer" else "NCCL all_to_all_single + index gathers" + exchange_note),
+            "rounds": {"count": args.rounds, "ms_per_step_min": min(round_ms), "ms_per_step_max": max(round_ms)},
+            "parity": parity, "nccl_exchange": nccl_exchange,
             "exchange_share": 1.0 - ms_gemm / ms_step, "ms_gemm_per_step": ms_gemm,
             "scaling_base": scaling_base,
             "cpu_baseline": None,
@@ -948,17 +1023,18 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="multi-GPU row exchange: peer-memory pushes (default) or NCCL all-to-all")
-    ap.add_argument("--overlap", action="store_true",
-                    help="multi-GPU runs: issue the exchanges on a second stream under the GEMMs "
-                         "(measured: +3 %% at 8 GPUs, -5 %% at 2 GPUs, so off by default)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="multi-GPU runs: keep both dispatches on the main stream (nothing hidden under the GEMMs)")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="multi-GPU runs: skip the check against the NCCL path and the fp32 products before timing")
+    ap.add_argument("--no-nccl-compare", action="store_true",
+                    help="multi-GPU runs: skip timing the same step with NCCL all-to-all as the exchange")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="multi-GPU runs: combine with separate push kernels instead of from the GEMM epilogues")
     ap.add_argument("--no-scaling-base", action="store_true",
-                    help="multi-GPU runs: skip timing the same workload on rank 0's GPU alone")
+                    help="skip timing the multi-GPU workload on one GPU (rank 0's) alone")
     ap.add_argument("--fused", action="store_true",
                     help="also time gmm_gather, gmm_swiglu and the weighted combine against separate torch kernels")
-    ap.add_argument("--scaling-base", action="store_true",
-                    help="also time the multi-GPU workload on this one GPU (strong-scaling denominator)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.traffic_from:

@@ -58,9 +58,13 @@ SIGNATURES = {
         _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
+    "b200gmm_run_swiglu_backward": (_c.c_int, [
+        _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
+        _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
+        _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
     "b200gmm_push_rows": (_c.c_int, [
         _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
-        _c.c_void_p]),
+        _c.c_int, _c.c_void_p]),
     "b200gmm_fill_offsets": (_c.c_int, [
         _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int,
         _c.c_void_p, _c.c_void_p]),

@@ -209,7 +209,7 @@ def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False, c=None):
     callers run ``gmm`` twice and apply the activation in a kernel of their own).
     Both products share one fp32 accumulator tile, the gate is applied to the
     fp32 values and the result is rounded to bf16 once, so neither product is
-    ever written to memory.  Forward only: no autograd.
+    ever written to memory.  ``fused.gmm_swiglu`` is the same with autograd.
 
     ``a`` bf16 [T, k] sorted by expert as for ``gmm``; ``b_gate`` and ``b_up``
     bf16 [z, k, n] (or [z, n, k] with ``trans_b``); returns ``c`` bf16 [T, n]."""
@@ -243,6 +243,41 @@ def gmm_swiglu(a, b_gate, b_up, batch_sizes, trans_b=False, c=None):
             backend.device_status(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
     _capi.check(rc, "b200gmm_run_swiglu")
     return c
+
+
+def gmm_swiglu_backward(a, b_gate, b_up, grad_out, batch_sizes, trans_b=False):
+    """Gradients of ``gmm_swiglu`` with respect to its two products, in one kernel
+    (no counterpart in the reference).  The gate and up products are recomputed in
+    the accumulator; returns ``(d_gate, d_up)``, bf16 [T, n] each (two halves of one
+    [2, T, n] tensor), with ``d_gate = grad_out * up * silu'(gate)`` and
+    ``d_up = grad_out * silu(gate)``.  Rows past ``sum(batch_sizes)`` are zeros."""
+    assert a.ndim == 2 and b_gate.ndim == 3 and b_up.ndim == 3 and batch_sizes.ndim == 1 and grad_out.ndim == 2
+    n = b_gate.shape[1] if trans_b else b_gate.shape[2]
+    k = b_gate.shape[2] if trans_b else b_gate.shape[1]
+    if not (a.is_cuda and b_gate.device == b_up.device == grad_out.device == a.device) or \
+            (batch_sizes.is_cuda and batch_sizes.device != a.device):
+        raise RuntimeError("gmm_swiglu_backward: a, b_gate, b_up, grad_out (and a CUDA batch_sizes) must be on one CUDA device")
+    if not (a.dtype == b_gate.dtype == b_up.dtype == grad_out.dtype == torch.bfloat16) or batch_sizes.dtype != torch.int64:
+        raise RuntimeError("gmm_swiglu_backward: a, b_gate, b_up, grad_out must be bfloat16, batch_sizes int64")
+    tokens = a.shape[0]
+    if b_gate.shape != b_up.shape or a.shape[1] != k or batch_sizes.shape[0] != b_gate.shape[0] \
+            or grad_out.shape != (tokens, n):
+        raise RuntimeError("gmm_swiglu_backward: shapes of a, b_gate, b_up, grad_out and batch_sizes do not fit together")
+    if not (a.is_contiguous() and b_gate.is_contiguous() and b_up.is_contiguous() and grad_out.is_contiguous()):
+        raise RuntimeError("gmm_swiglu_backward: a, b_gate, b_up and grad_out must be contiguous")
+    out = torch.zeros(2, tokens, n, device=a.device, dtype=a.dtype)
+    lib = _capi.load()
+    z = batch_sizes.shape[0]
+    with torch.cuda.device(a.device):
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device)
+        bs = _host_or_device_sizes(batch_sizes)
+        rc = lib.b200gmm_run_swiglu_backward(
+            a.data_ptr(), b_gate.data_ptr(), b_up.data_ptr(), grad_out.data_ptr(), out.data_ptr(), bs.data_ptr(),
+            1 if bs.is_cuda else 0, z, tokens, k, n, 1 if trans_b else 0, ws.data_ptr(), ws_bytes,
+            backend.device_status(a.device).data_ptr(), torch.cuda.current_stream(a.device).cuda_stream)
+    _capi.check(rc, "b200gmm_run_swiglu_backward")
+    return out[0], out[1]
 
 
 def device_status(device="cuda"):

@@ -91,6 +91,7 @@ struct LaunchArgs {
   const __nv_bfloat16* a_src = nullptr;
   int64_t a_src_rows = 0;
   int64_t dest_lo = 0, dest_hi = 0;       // window every row_dest entry must fall into (0, 0: unchecked)
+  const __nv_bfloat16* gate_grad = nullptr;  // gated product: output gradient, selects the backward epilogue
 };
 
 template <int MODE, int CTAS, bool GATHER, bool SWIGLU>
@@ -109,7 +110,7 @@ cudaError_t launch_gmm(const LaunchArgs& a) {
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, a.map_a, a.map_b, a.map_b2, a.map_c, a.map_a2, a.c,
                             a.batch_sizes, a.p, a.status, a.slots, a.sched_counter, a.row_dest, a.a_rows, a.a_src, a.a_src_rows,
-                            a.row_scale, a.reduce_add, a.dest_lo, a.dest_hi);
+                            a.row_scale, a.reduce_add, a.dest_lo, a.dest_hi, a.gate_grad);
 }
 
 // The layout (a.p.mode) picks the last template argument; the gated product has no wgrad form.
@@ -233,8 +234,8 @@ int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
 int choose_ctas(int z, int64_t tokens, int64_t d1, int trans_a) {
   const int forced = env_int("B200GMM_CTAS", 0);
   if (forced == 1 || forced == 2) return forced;
-  if (trans_a) return d1 >= 256 ? 2 : 1;
-  return (z > 0 && tokens / z >= 512) ? 2 : 1;
+  if (z <= 0 || tokens / z < 512) return 1;
+  return (!trans_a || d1 >= 256) ? 2 : 1;
 }
 
 // Which kernel features a plain, gathered or gated launch uses (schedule.cuh: Problem).
@@ -261,12 +262,11 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   p->tile_m = kBlockM * ctas;
   p->group_m = env_int("B200GMM_GROUP_M", ctas == 2 ? 8 : 16);
   if (p->group_m < 1) p->group_m = 1;
-  // Tiles are drawn from a global counter.  Where tile durations differ widely
-  // (wgrad: the contraction is the expert's row count; one-CTA kernels: fine-grained
-  // experts, some a few rows, some thousands) the experts are also sorted by size and
-  // taken from both ends at once.
+  // Tiles are drawn from a global counter.  For wgrad, where a tile's duration is
+  // its expert's row count, the experts are taken largest first, so that the
+  // CTAs that finish early find short tiles left.
   p->dynamic = env_int("B200GMM_DYNAMIC", 1) != 0;
-  p->order = (p->dynamic && z > 1 && (p->mode == kTN || ctas == 1)) ? env_int("B200GMM_ORDER", 1) : 0;
+  p->order = (p->dynamic && z > 1 && p->mode == kTN) ? env_int("B200GMM_ORDER", 1) : 0;
   p->light = (p->mode != kTN && ctas == 1 && !f.gather && !f.swiglu) ? env_int("B200GMM_LIGHT", 1) : 0;
   const int64_t wait_ns = env_int64("B200GMM_WAIT_LIMIT_NS", static_cast<int64_t>(ptx::kWaitLimitNs));
   p->wait_ns = wait_ns > 0 ? wait_ns : static_cast<int64_t>(ptx::kWaitLimitNs);
@@ -277,6 +277,12 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
                                     : (tokens / p->tile_m + 3 * int64_t(z));  // + transposed tiles, half as wide
   if (row_tiles * nt >= (int64_t(1) << 30)) return B200GMM_ELIMIT;
   return B200GMM_OK;
+}
+
+// Argument checks alone (no launch): what run_impl would refuse for these sizes.
+int check_args_only(int z, int64_t tokens, int64_t d1, int64_t n, int trans_b) {
+  Problem p;
+  return check_problem(z, tokens, d1, n, 0, trans_b, 1, &p);
 }
 
 size_t round128(size_t x) { return (x + 127) & ~size_t(127); }
@@ -344,7 +350,10 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              uint32_t* device_status, void* cuda_stream, const int64_t* row_dest,
              const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr,
              const float* row_scale = nullptr, int reduce_add = 0, const void* dest_base = nullptr,
-             int64_t dest_bytes = 0) {
+             int64_t dest_bytes = 0, const void* gate_grad = nullptr) {
+  // gate_grad != nullptr: backward epilogue of the gated product; c is [2, tokens, n].
+  if (gate_grad != nullptr && (b2 == nullptr || row_dest != nullptr || (reinterpret_cast<uintptr_t>(gate_grad) & 15)))
+    return B200GMM_EINVAL;
   if (dest_base != nullptr && (row_dest == nullptr || dest_bytes < 0)) return B200GMM_EINVAL;
   if ((row_scale != nullptr || reduce_add) && row_dest == nullptr) return B200GMM_EINVAL;
   if (a_rows != nullptr && (dim_a1 == 0 || a_source_rows <= 0 || (trans_a && row_dest != nullptr)))
@@ -471,15 +480,16 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   if (!have_b2) map_b2 = map_b;  // unused by the kernel, but a valid map
   if (!p.light) map_a2 = map_a;
 
-  // Output map for the epilogue's TMA stores: 32 x 32 boxes, 64-byte swizzle.
-  // wgrad's c[z, m, n] is addressed as z*m rows.  Unused (left zeroed) when the
-  // rows are scattered through row_dest.
+  // Output map for the epilogue's TMA stores: 32 x 32 boxes, 64-byte swizzle; for
+  // wgrad, whose c[z, m, n] is addressed as z*m rows, 64 x 32 boxes with 128-byte
+  // swizzle.  Unused (left zeroed) when the rows are scattered through row_dest.
   CUtensorMap map_c = {};
   if (row_dest == nullptr) {
-    const uint64_t dc[2] = {N, p.mode == kTN ? Z * D1 : T};
-    const uint32_t bc[2] = {32, 32};
+    const uint64_t dc[2] = {N, p.mode == kTN ? Z * D1 : (gate_grad != nullptr ? 2 * T : T)};
+    const uint32_t bc[2] = {p.mode == kTN ? 64u : 32u, 32};
     if (dc[1] >= (uint64_t(1) << 31)) return B200GMM_ELIMIT;
-    if ((rc = encode_map(&map_c, c, 2, dc, bc, CU_TENSOR_MAP_SWIZZLE_64B)) != 0) return rc;
+    if ((rc = encode_map(&map_c, c, 2, dc, bc, p.mode == kTN ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B)) != 0)
+      return rc;
   }
 
   LaunchArgs la;
@@ -500,6 +510,7 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   la.row_dest = row_dest;
   la.row_scale = row_scale;
   la.reduce_add = reduce_add;
+  la.gate_grad = static_cast<const __nv_bfloat16*>(gate_grad);
   if (dest_base != nullptr) {
     la.dest_lo = static_cast<int64_t>(reinterpret_cast<uintptr_t>(dest_base));
     la.dest_hi = la.dest_lo + dest_bytes;
@@ -595,6 +606,25 @@ int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void
                   dest_bytes);
 }
 
+int b200gmm_run_swiglu_backward(const void* a, const void* b_gate, const void* b_up, const void* grad_out,
+                                void* grad_products, const int64_t* batch_sizes, int batch_sizes_on_device, int z,
+                                int64_t tokens, int64_t dim_a1, int64_t n, int trans_b, void* workspace,
+                                size_t workspace_bytes, uint32_t* device_status, void* cuda_stream) {
+  if (grad_products == nullptr || (grad_out == nullptr && tokens > 0 && n > 0)) return B200GMM_EINVAL;
+  if (b_up == nullptr && tokens > 0 && n > 0 && dim_a1 > 0 && z > 0) return B200GMM_EINVAL;
+  if (dim_a1 == 0 || tokens == 0 || n == 0 || z == 0) {
+    // g = u = 0 everywhere: dg = dh * 0 * silu'(0) = 0 and du = dh * silu(0) = 0
+    if (tokens > 0 && n > 0 && z > 0 &&
+        cudaMemsetAsync(grad_products, 0, size_t(2) * size_t(tokens) * size_t(n) * 2,
+                        static_cast<cudaStream_t>(cuda_stream)) != cudaSuccess)
+      return B200GMM_ECUDA;
+    return check_args_only(z, tokens, dim_a1, n, trans_b);
+  }
+  return run_impl(a, b_gate, grad_products, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
+                  workspace, workspace_bytes, device_status, cuda_stream, nullptr, nullptr, 0, b_up, nullptr, 0, nullptr, 0,
+                  grad_out);
+}
+
 int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* batch_sizes,
                        int batch_sizes_on_device, int z, int64_t tokens, int64_t dim_a1, int64_t n,
                        int trans_a, int trans_b, uint32_t* device_status, void* cuda_stream) {
@@ -608,7 +638,7 @@ int b200gmm_run_static(const void* a, const void* b, void* c, const int64_t* bat
 
 int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items, const int32_t* src_row,
                       const int32_t* dst_rank, const int64_t* dst_row, const void* const* peer_base,
-                      void* cuda_stream) {
+                      int max_ctas, void* cuda_stream) {
   if (row_bytes <= 0 || (row_bytes % 16) != 0 || n_items < 0) return B200GMM_EINVAL;
   if (n_items == 0) return B200GMM_OK;
   if (src == nullptr || dst_rank == nullptr || dst_row == nullptr || peer_base == nullptr)
@@ -622,7 +652,10 @@ int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items, const
   // launched on another stream can become resident next to this one (8 CTAs of
   // 256 threads would fill an SM's 2048 thread slots and lock the GEMM out until
   // the whole transfer is done).
+  // max_ctas > 0 caps the grid for a transfer that is meant to trickle along under
+  // a GEMM on another stream without taking its memory bandwidth.
   int64_t grid = int64_t(dev->sm_count) * 4;
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid > n_items) grid = n_items;
   push_rows_kernel<<<static_cast<unsigned>(grid), kPushThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
       static_cast<const uint4*>(src), row_bytes / 16, n_items, src_row, dst_rank, dst_row,
@@ -679,20 +712,11 @@ int b200gmm_schedule_host(const int64_t* batch_sizes_host, int z, int64_t tokens
   for (int i = 0; i < z; ++i)
     tile_start[i + 1] = tile_start[i] + expert_tiles(p, row_start[perm[i] + 1] - row_start[perm[i]]);
   const int total = tile_start[z];
-  int front = 0, back = z > 0 ? z - 1 : 0;
+  int pos = 0;
   for (int t = 0; t < total && out != nullptr && t < max_tiles; ++t) {
-    int stream;
-    const int q = order_index(p.order, t, total, &stream);
-    int pos;
-    if (stream == 0) {
-      while (q >= tile_start[front + 1]) ++front;
-      pos = front;
-    } else {
-      while (q < tile_start[back]) --back;
-      pos = back;
-    }
+    while (t >= tile_start[pos + 1]) ++pos;
     const int e = perm[pos];
-    const Tile tile = make_tile(p, e, q - tile_start[pos], row_start[e], row_start[e + 1]);
+    const Tile tile = make_tile(p, e, t - tile_start[pos], row_start[e], row_start[e + 1]);
     int64_t* o = out + int64_t(t) * B200GMM_SCHEDULE_FIELDS;
     o[0] = tile.expert;
     o[1] = tile.row0;

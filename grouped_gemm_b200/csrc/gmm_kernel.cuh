@@ -66,9 +66,9 @@ constexpr uint32_t kTmemCols = 512;
 constexpr int kMaxStages = 6;
 constexpr uint32_t kBoxBytes = 64 * kBlockK * 2;  // one 64-wide MN-major TMA box: 8 KiB
 // wgrad keeps private, editable copies of its two tensor maps in the caller's
-// workspace: kMapSlots {a, b} pairs per cluster.  The scheduler edits a slot only
-// when it is not the current map of one of the two tile streams and every tile that
-// used it has all its loads landed (the MMA warp counts finished tiles).
+// workspace: kMapSlots {a, b} pairs per cluster, edited in turn.  The scheduler
+// edits a slot only when every tile that used it has all its loads landed (the
+// MMA warp counts finished tiles).
 constexpr int kMapSlots = 8;
 constexpr int kMaxCtas = 256;  // workspace is sized for this many CTAs
 // Ring through which the scheduler hands tile positions to the other roles.  Deep
@@ -77,19 +77,23 @@ constexpr int kMaxCtas = 256;  // workspace is sized for this many CTAs
 // a tensor-map edit) stay hidden behind tiles already handed out.
 constexpr int kSchedSlots = 8;
 
-// wgrad gives up one ring stage for a second epilogue staging buffer per warp: its
-// tiles can be a single k-block deep (few rows per expert, or none), and then the
-// kernel runs at the speed of its output stores.
+// wgrad gives up ring stages for larger epilogue staging: its tiles can be a single
+// k-block deep (few rows per expert, or none), and then the kernel runs at the
+// speed of its output stores.  Each epilogue warp has two buffers of 32 rows x 64
+// columns there (128-byte rows), used in turn, so that a warp fills one while
+// the TMA store of the other still reads; the forward / dgrad layouts have one
+// buffer of 32 x 32 per warp.
 template <int CTAS, int MODE = kNN>
 struct Geometry {
-  static constexpr int kStages = (MODE == kTN) ? ((CTAS == 1) ? 3 : 5) : ((CTAS == 1) ? 4 : 6);
+  static constexpr int kStages = (MODE == kTN) ? ((CTAS == 1) ? 3 : 4) : ((CTAS == 1) ? 4 : 6);
   static constexpr int kOutBufs = (MODE == kTN) ? 2 : 1;  // staging buffers per epilogue warp
+  static constexpr uint32_t kOutBufBytes = (MODE == kTN) ? 4096u : 2048u;
   static constexpr int kBCols = kBlockN / CTAS;                 // B columns staged by one CTA
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;    // 16 KiB
   static constexpr uint32_t kBBytes = kBCols * kBlockK * 2;     // 32 or 16 KiB
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB (wgrad: 160 or 144 KiB)
-  static constexpr uint32_t kOutBytes = kEpilogueWarps * kOutBufs * 2048u;  // 16 KiB (wgrad: 32 KiB)
+  static constexpr uint32_t kRingBytes = kStages * kStageBytes;  // 192 KiB (wgrad: 128 or 144 KiB)
+  static constexpr uint32_t kOutBytes = kEpilogueWarps * kOutBufs * kOutBufBytes;  // 16 KiB (wgrad: 64 KiB)
 };
 
 // A transposed tile's stage inside a one-CTA ring slot: 128 columns x 128 k of the
@@ -106,12 +110,6 @@ static_assert(kLightWBytes + 2 * kLightXHalf <= Geometry<1>::kStageBytes, "a tra
 template <int CTAS, int MODE = kNN>
 constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS, MODE>::kStages; }
 
-// Epilogue staging: per epilogue warp one buffer (wgrad: two, used in turn) of 32
-// rows x 32 bf16 columns (64-byte rows, 64-byte swizzle), the source of its TMA
-// stores.  A warp converts its next chunk in registers while the previous store
-// still reads the buffer.
-constexpr uint32_t kStageOutBytes = 32 * 32 * 2;                  // 2 KiB
-static_assert(kStageOutBytes == 2048u, "Geometry::kOutBytes assumes 2 KiB buffers");
 
 struct __align__(8) SmemTail {
   uint64_t full[kMaxStages];
@@ -168,7 +166,8 @@ __device__ __forceinline__ int64_t scan_step(int64_t v, int lane, int64_t* carry
 //               that a bad batch_sizes can never push a store out of bounds;
 //   perm        the experts in launch order: by index, or (order == 1) by number
 //               of rows, largest first, ties by index (the reference sorts its
-//               wgrad problems the same way, csrc/fill_arguments.cuh:80-86);
+//               wgrad problems the same way, csrc/fill_arguments.cuh:80-86), so
+//               that the launch ends on the shortest tiles;
 //   tile_start  exclusive prefix sums of the per-expert tile counts in that order.
 __device__ __forceinline__ void build_schedule(const Problem& p, const int64_t* __restrict__ batch_sizes,
                                                SmemTail* tail, uint32_t* status) {
@@ -228,31 +227,19 @@ __device__ __forceinline__ void build_schedule(const Problem& p, const int64_t* 
 }
 
 // Position of the launch order -> tile.  Every role keeps its own copy; positions
-// arrive in increasing order, so the expert cursors of the two streams (front of
-// the order, back of the order) only ever move one way.
+// arrive in increasing order, so the expert cursor only ever moves forward.
 struct TileWalker {
   const Problem& p;
   const SmemTail* tail;
   int total;
-  int pos_front;
-  int pos_back;
+  int pos;
   __device__ TileWalker(const Problem& p_, const SmemTail* tail_)
-      : p(p_), tail(tail_), total(tail_->tile_start[p_.z]), pos_front(0), pos_back(p_.z > 0 ? p_.z - 1 : 0) {}
+      : p(p_), tail(tail_), total(tail_->tile_start[p_.z]), pos(0) {}
   __device__ __forceinline__ bool decode(int t, Tile* out) {
     if (t < 0 || t >= total) return false;
-    int stream;
-    const int q = order_index(p.order, t, total, &stream);
-    int pos;
-    if (stream == 0) {
-      while (q >= tail->tile_start[pos_front + 1]) ++pos_front;
-      pos = pos_front;
-    } else {
-      while (q < tail->tile_start[pos_back]) --pos_back;
-      pos = pos_back;
-    }
+    while (t >= tail->tile_start[pos + 1]) ++pos;
     const int e = tail->perm[pos];
-    *out = make_tile(p, e, q - tail->tile_start[pos], tail->row_start[e], tail->row_start[e + 1]);
-    out->stream = stream;
+    *out = make_tile(p, e, t - tail->tile_start[pos], tail->row_start[e], tail->row_start[e + 1]);
     return true;
   }
 };
@@ -317,7 +304,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
            uint32_t* status, CUtensorMap* map_slots, uint32_t* sched_counter, const int64_t* __restrict__ row_dest,
            const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
            const int64_t a_src_rows, const float* __restrict__ row_scale, const int reduce_add,
-           const int64_t dest_lo, const int64_t dest_hi) {
+           const int64_t dest_lo, const int64_t dest_hi, const __nv_bfloat16* __restrict__ gate_grad) {
   static_assert(!SWIGLU || MODE != kTN, "the gated product is a forward product");
   // SWIGLU: two right operands of n columns each, b (gate) and b2 (up).  The
   // schedule runs over 2n virtual columns, 256 per tile: accumulator columns
@@ -644,12 +631,11 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         TileWalker walk(p, tail);
         TileFeed<kPair> feed(tail, wait);
         Tile t;
-        // wgrad: the map slot and expert of each of the two tile streams, the slot
-        // edited last, and for every slot the index (in this cluster's sequence of
-        // tiles) of the last tile that loads through it.
-        int held_expert[2] = {-1, -1};
-        int held_slot[2] = {-1, -1};
-        int last_slot = 0;
+        // wgrad: the map slot clipped to the current expert, and for every slot the
+        // index (in this cluster's sequence of tiles) of the last tile that loads
+        // through it.
+        int held_expert = -1;
+        int held_slot = 0;
         int last_tile[kMapSlots];
 #pragma unroll
         for (int i = 0; i < kMapSlots; ++i) last_tile[i] = -1;
@@ -662,36 +648,25 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           int entry = 0;
           const bool live = walk.decode(pos, &t);
           if (MODE == kTN && live && t.k_len > 0) {
-            const int st = t.stream;
-            if (held_expert[st] != t.expert) {
-              // New expert on this stream: clip the row extent of a and b at its last
-              // row in a copy that neither stream uses and no unfinished tile loads
-              // through.  With kMapSlots copies one is free as soon as the MMA warp has
-              // caught up far enough; until then, wait (the tiles in question have been
-              // handed out already and finish on their own).
-              int slot = -1;
+            if (held_expert != t.expert) {
+              // New expert: clip the row extent of a and b at its last row, in the next
+              // copy of the maps.  That copy may only be edited once every tile that
+              // loaded through it has all its loads landed; with kMapSlots copies this
+              // is a wait only when the MMA warp is that many experts behind (the tiles
+              // in question have been handed out already and finish on their own).
+              const int slot = (held_slot + 1) % kMapSlots;
               const uint64_t t0 = ptx::globaltimer_ns();
-              while (slot < 0) {
-                const int done = static_cast<int>(*reinterpret_cast<volatile uint32_t*>(&tail->tiles_done));
-                int cand = last_slot;
-#pragma unroll
-                for (int i = 0; i < kMapSlots; ++i) {
-                  cand = (cand + 1) % kMapSlots;
-                  if (slot < 0 && cand != held_slot[0] && cand != held_slot[1] && last_tile[cand] < done) slot = cand;
+              while (last_tile[slot] >= static_cast<int>(*reinterpret_cast<volatile uint32_t*>(&tail->tiles_done))) {
+                if (tail->abort_flag || ptx::globaltimer_ns() - t0 > wait.limit_ns) {
+                  tail->abort_flag = 1u;
+                  ok = false;
+                  break;
                 }
-                if (slot < 0) {
-                  if (tail->abort_flag || ptx::globaltimer_ns() - t0 > wait.limit_ns) {
-                    tail->abort_flag = 1u;
-                    ok = false;
-                    break;
-                  }
-                  __nanosleep(64);
-                }
+                __nanosleep(64);
               }
               if (!ok) break;
-              last_slot = slot;
-              held_expert[st] = t.expert;
-              held_slot[st] = slot;
+              held_expert = t.expert;
+              held_slot = slot;
               CUtensorMap* ea = my_maps + slot * 2;
               CUtensorMap* eb = ea + 1;
               const uint32_t rows_end = static_cast<uint32_t>(t.k_row0 + t.k_len);
@@ -700,10 +675,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               ptx::fence_tensormap_release();
               entry = kMapFresh;
             }
-            entry |= held_slot[st];
-#pragma unroll
-            for (int i = 0; i < kMapSlots; ++i)
-              if (i == held_slot[st]) last_tile[i] = static_cast<int>(feed.taken);
+            entry |= held_slot;
+            last_tile[held_slot] = static_cast<int>(feed.taken);
           }
           if (!feed.publish(pos, entry)) { ok = false; break; }
           if (!live) break;  // the end of the order has been handed to everyone
@@ -850,7 +823,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const int q = warp & 3;            // TMEM lane quadrant this warp may read
     const int half = (warp - 2) >> 2;  // which 128 of the tile's 256 columns
     const int col_base = half * (kBlockN / 2);
-    const uint32_t my_out = out_base + uint32_t(warp - 2) * (kStageOutBytes * G::kOutBufs);
+    const uint32_t my_out = out_base + uint32_t(warp - 2) * (G::kOutBufBytes * G::kOutBufs);
     TileWalker walk(p, tail);
     TileFeed<kPair> feed(tail, wait);
     Tile t;
@@ -866,16 +839,14 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     };
     // Buffer for the next TMA store and the wait before it may be written: with two
     // buffers the store before last read this one.
-    auto stage_buf = [&]() { return my_out + (G::kOutBufs == 2 ? (stores & 1u) * kStageOutBytes : 0u); };
+    auto stage_buf = [&]() { return my_out + (G::kOutBufs == 2 ? (stores & 1u) * G::kOutBufBytes : 0u); };
 
     // One 32-column chunk `v` (fp32 bits) of this lane's row, starting at column
     // `col` of the tile: through the staging buffer and a TMA store when the
     // whole warp's rows exist, else straight to global for the rows that do.
     const bool scatter_rows = (MODE != kTN) && (row_dest != nullptr);
-    auto emit = [&](const uint32_t (&v)[32], int col, bool warp_full, bool row_ok,
-                    __nv_bfloat16* crow, int cols_left, int tile_row, int col0) {
-      if (col >= cols_left) return;  // chunk lies entirely past the last column
-      uint4 o[4];
+    // 32 fp32 values -> 32 bf16 in four 16-byte pieces
+    auto pack = [](const uint32_t (&v)[32], uint4* o) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         __nv_bfloat162 h;
@@ -888,7 +859,41 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         h = __floats2bfloat162_rn(__uint_as_float(v[j * 8 + 6]), __uint_as_float(v[j * 8 + 7]));
         o[j].w = *reinterpret_cast<uint32_t*>(&h);
       }
-      if (warp_full) {
+    };
+    // wgrad, all 32 rows of the warp exist: 64 columns (two chunks) through one
+    // staging buffer of 128-byte rows (128-byte swizzle: 16-byte piece index ^=
+    // row % 8) and one TMA store of a 64 x 32 box; columns past the tensor's last
+    // are clipped by the store.
+    auto emit64 = [&](const uint32_t (&v0)[32], const uint32_t (&v1)[32], int col, int tile_row, int col0) {
+      uint4 o[8];
+      pack(v0, o);
+      pack(v1, o + 4);
+      const uint32_t buf = stage_buf();
+      if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<G::kOutBufs - 1>();
+      __syncwarp();
+      const uint32_t row_addr = buf + uint32_t(lane) * 128u;
+      const uint32_t sw = uint32_t(lane) & 7u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t dst = row_addr + ((uint32_t(j) ^ sw) << 4);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(o[j].x), "r"(o[j].y),
+                     "r"(o[j].z), "r"(o[j].w)
+                     : "memory");
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::tma_store_2d(&map_c, buf, col0 + col, tile_row);
+        ptx::bulk_commit_group();
+      }
+      ++stores;
+    };
+    auto emit = [&](const uint32_t (&v)[32], int col, bool warp_full, bool row_ok,
+                    __nv_bfloat16* crow, int cols_left, int tile_row, int col0) {
+      if (col >= cols_left) return;  // chunk lies entirely past the last column
+      uint4 o[4];
+      pack(v, o);
+      if (MODE != kTN && warp_full) {
         // The store that last read this buffer must be done reading.
         const uint32_t buf = stage_buf();
         if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<G::kOutBufs - 1>();
@@ -1030,17 +1035,17 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           const uint32_t buf = stage_buf();
           if (lane == 0 && stores > 0) ptx::bulk_wait_group_read<G::kOutBufs - 1>();
           __syncwarp();
-          const uint32_t row_addr = buf + uint32_t(lane) * 64u;
+          const uint32_t row_addr = buf + uint32_t(lane) * 128u;
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
+          for (int j = 0; j < 8; ++j)
             asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};" ::"r"(row_addr + (uint32_t(j) << 4)), "r"(0u)
                          : "memory");
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) {
 #pragma unroll 1
-            for (int ch = 0; ch < kBlockN / 64; ++ch) {
-              const int col = col_base + ch * 32;
+            for (int ch = 0; ch < kBlockN / 128; ++ch) {
+              const int col = col_base + ch * 64;
               if (col < cols_left) ptx::tma_store_2d(&map_c, buf, t.col0 + col, tile_row);
             }
             ptx::bulk_commit_group();
@@ -1078,6 +1083,36 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               else ptx::mbar_arrive(te_bar);
             }
           }
+          const int col = half * 64 + ch * 32;
+          if (gate_grad != nullptr) {
+            // Backward of the gated product: with g, u recomputed in the accumulator and
+            // dh = gate_grad[row, col ..] read here, the gradients w.r.t. the two products
+            //   dg = dh * u * silu'(g),  silu'(g) = s (1 + g (1 - s)),  s = 1 / (1 + exp(-g))
+            //   du = dh * silu(g)
+            // go to rows [0, T) and [T, 2T) of the output.
+            uint4 d4[4] = {};
+            if (row_ok) {
+              const uint4* src = reinterpret_cast<const uint4*>(gate_grad + (out_row0 + r) * out_n + out_col0 + col);
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (col + j * 8 < cols_left) d4[j] = src[j];
+            }
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(d4);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float g = __uint_as_float(va[i]);
+              const float u = __uint_as_float(vb[i]);
+              const float2 dpair = __bfloat1622float2(d2[i >> 1]);
+              const float dh = (i & 1) ? dpair.y : dpair.x;
+              const float sg = __fdividef(1.0f, 1.0f + __expf(-g));
+              va[i] = __float_as_uint(dh * u * sg * (1.0f + g * (1.0f - sg)));
+              vb[i] = __float_as_uint(dh * g * sg);
+            }
+            emit(va, col, warp_full, row_ok, crow, cols_left, tile_row, out_col0);
+            emit(vb, col, warp_full, row_ok, crow + p.tokens * out_n, cols_left, tile_row + static_cast<int>(p.tokens),
+                 out_col0);
+            continue;
+          }
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const float g = __uint_as_float(va[i]);
@@ -1085,11 +1120,31 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
             va[i] = __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * u);  // silu(g) * u
           }
           if (scaled) scale(va);
-          emit(va, half * 64 + ch * 32, warp_full, row_ok, crow, cols_left, tile_row, out_col0);
+          emit(va, col, warp_full, row_ok, crow, cols_left, tile_row, out_col0);
         }
         continue;
       }
       const uint32_t taddr = tmem_base + (uint32_t(q * 32) << 16) + ab * kBlockN + col_base;
+      if (MODE == kTN && warp_full) {
+#pragma unroll 1
+        for (int ch = 0; ch < kBlockN / 64; ch += 2) {
+          ptx::tmem_ld_32x32(taddr + ch * 32, va);
+          ptx::tmem_ld_32x32(taddr + (ch + 1) * 32, vb);
+          ptx::tmem_ld_wait();
+          if (ch + 2 >= kBlockN / 64) {
+            // Every column has been read: hand the accumulator back before the last store.
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+              const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
+              if (kPair) ptx::mbar_arrive_cluster(ptx::mapa(te_bar, 0));
+              else ptx::mbar_arrive(te_bar);
+            }
+          }
+          if (col_base + ch * 32 < cols_left) emit64(va, vb, col_base + ch * 32, tile_row, t.col0);
+        }
+        continue;
+      }
       ptx::tmem_ld_32x32(taddr, va);
 #pragma unroll 1
       for (int ch = 0; ch < kBlockN / 64; ch += 2) {

@@ -29,12 +29,13 @@ constexpr int kBlockM = 128;  // output rows per CTA (UMMA M per CTA)
 constexpr int kBlockN = 256;  // output tile cols   (UMMA N)
 constexpr int kBlockK = 64;   // k depth per pipeline stage = one 128-byte swizzle row of bf16
 
-// Transposed ("swap-AB") tiles of the forward / dgrad layouts: the last rows of an
-// expert, when there are at most kLightRows of them, do not get a 128-row tile of
-// their own.  Instead 128 output COLUMNS ride the UMMA M dimension and the few
-// rows ride UMMA N (a multiple of 16), so a 5-row expert costs an N=16 instruction
-// instead of a padded 128 x 256 one.  Such a tile is kLightCols columns wide and
-// takes kLightK of the contraction per pipeline stage.
+// Transposed ("swap-AB") tiles of the forward / dgrad layouts: an expert with at
+// most kLightRows rows does not get a 128-row tile.  Instead 128 output COLUMNS
+// ride the UMMA M dimension and the few rows ride UMMA N (a multiple of 16), so a
+// 5-row expert costs an N=16 instruction instead of a padded 128 x 256 one.  Such a
+// tile is kLightCols columns wide and takes kLightK of the contraction per pipeline
+// stage.  (Larger experts keep 128-row tiles for their last rows too: a transposed
+// tile for the remainder would sweep the expert's weights a second time.)
 constexpr int kLightRows = 64;
 constexpr int kLightCols = 128;
 constexpr int kLightK = 128;
@@ -47,9 +48,8 @@ struct Problem {
   int64_t n;       // output columns
   int tile_m;      // output rows per scheduled tile: 128 (one CTA) or 256 (a CTA pair)
   int group_m;     // row-tiles swept together across the columns (L2 reuse of b)
-  int light;       // 1: row remainders of <= kLightRows rows run as transposed tiles (NN/NT, tile_m 128)
-  int order;       // 0: experts in index order.  1: experts sorted by rows, largest first, and
-                   //    tiles taken alternately from the front and from the back of that order
+  int light;       // 1: experts of <= kLightRows rows run as transposed tiles (NN/NT, tile_m 128)
+  int order;       // 0: experts in index order.  1: experts sorted by rows, largest first
   int dynamic;     // 1: CTAs draw positions of the launch order from a global counter
   int64_t wait_ns; // limit of every wait inside the kernel, in nanoseconds
 };
@@ -62,24 +62,20 @@ struct Tile {
   int k_row0;      // TN: first contraction row in a/b (global); else 0
   int k_len;       // contraction length (k, or batch_sizes[expert] for TN)
   int kind;        // 0: tile_m x 256 tile; 1: transposed tile (valid_rows <= kLightRows, kLightCols columns)
-  int stream;      // order == 1: 0 = taken from the front of the order, 1 = from the back
 };
 
 B200GMM_HD int ceil_div_i(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
 
 B200GMM_HD int col_tiles(const Problem& p) { return ceil_div_i(p.n, kBlockN); }
 
-// Row-tiles of tile_m rows an expert with `rows` rows gets, and the rows left over
-// for a transposed tile (0 if none).
+// Row-tiles of tile_m rows an expert with `rows` rows gets, and the rows that go
+// to transposed tiles instead (0 if none).
 B200GMM_HD int heavy_row_tiles(const Problem& p, int64_t rows) {
-  if (!p.light) return ceil_div_i(rows, p.tile_m);
-  const int rem = static_cast<int>(rows % kBlockM);
-  return static_cast<int>(rows / kBlockM) + (rem > kLightRows ? 1 : 0);
+  if (p.light && rows <= kLightRows) return 0;
+  return ceil_div_i(rows, p.tile_m);
 }
 B200GMM_HD int light_rows(const Problem& p, int64_t rows) {
-  if (!p.light) return 0;
-  const int rem = static_cast<int>(rows % kBlockM);
-  return rem <= kLightRows ? rem : 0;
+  return (p.light && rows <= kLightRows) ? static_cast<int>(rows) : 0;
 }
 
 // Tiles of one expert.  TN always has the full c[i] grid (empty experts still
@@ -113,7 +109,6 @@ B200GMM_HD Tile make_tile(const Problem& p, int expert, int local, int rs, int r
   Tile t;
   t.expert = expert;
   t.kind = 0;
-  t.stream = 0;
   const int nt = col_tiles(p);
   int mi, ni;
   if (p.mode == kTN) {
@@ -143,18 +138,6 @@ B200GMM_HD Tile make_tile(const Problem& p, int expert, int local, int rs, int r
     t.col0 = (local - mt * nt) * kLightCols;
   }
   return t;
-}
-
-// Position `t` of the launch order -> index into the sequence of all tiles laid
-// out expert after expert in `perm` order.  With order == 1 even positions walk
-// that sequence from the front (largest experts: long, tensor-bound tiles) and odd
-// positions from the back (smallest experts: short tiles bound by the weight or
-// output traffic), so both kinds are in flight at any time and the launch ends
-// on mid-sized tiles.
-B200GMM_HD int order_index(int order, int t, int total, int* stream) {
-  if (!order) { *stream = 0; return t; }
-  *stream = t & 1;
-  return (t & 1) ? total - 1 - (t >> 1) : (t >> 1);
 }
 
 // The nine per-expert values of the reference's GemmProblem

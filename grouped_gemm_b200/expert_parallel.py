@@ -158,7 +158,8 @@ class PeerExchange:
     """Plan + symmetric buffers for one routing.
 
     Buffers (all in one symmetric allocation per rank, same size on every rank):
-      ``a_grouped``  [cap, h_in]   dispatch target, rows grouped by local expert
+      ``a_grouped``  [cap, h_in]   dispatch target, rows grouped by local expert (two of them,
+                                   used in turn when the next step's dispatch is issued ahead)
       ``g_grouped``  [cap, h_out]  dispatch target for output gradients
       ``out_slots``  [pairs, h_out] combine target, (token, slot) order
       ``da_slots``   [pairs, h_in]  combine target for dgrad rows
@@ -234,7 +235,7 @@ class PeerExchange:
         def align(n):
             return (n + 255) // 256 * 256
         sizes = [self.cap * h_in * esize, self.cap * h_out * esize, self.pairs_cap * h_out * esize,
-                 self.pairs_cap * h_in * esize, self.cap * 16]
+                 self.pairs_cap * h_in * esize, self.cap * 16, self.cap * h_in * esize]
         offs, total = [], 0
         for n in sizes:
             offs.append(total)
@@ -256,8 +257,9 @@ class PeerExchange:
             n = rows * cols * torch.empty(0, dtype=dt).element_size()
             return self._symm[off:off + n].view(dt).view(rows, cols)
 
-        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin = (table(o) for o in offs)
+        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin, self._t_a2 = (table(o) for o in offs)
         self.a_grouped = view(offs[0], self.cap, h_in, dtype)
+        self.a_grouped2 = view(offs[5], self.cap, h_in, dtype)   # second dispatch target, for a dispatch issued ahead
         self.g_grouped = view(offs[1], self.cap, h_out, dtype)
         self.out_slots = view(offs[2], self.pairs_cap, h_out, dtype)
         self.da_slots = view(offs[3], self.pairs_cap, h_in, dtype)
@@ -282,20 +284,26 @@ class PeerExchange:
         self.dest_da = (da_bases + self.back_row * (h_in * esize)).contiguous()
         self._ws_bytes = _capi.workspace_bytes(self.per_rank)
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._ahead = None       # (data_ptr of the x dispatched ahead, buffer index, event)
+        self._cur = 0            # which a_grouped buffer the current step reads
+        # Blocks of a push that runs under a GEMM: enough to keep NVLink busy, few
+        # enough to leave the GEMM its memory bandwidth.
+        self.side_push_ctas = 32
 
     # -- plumbing ---------------------------------------------------------------
-    def barrier(self):
+    def barrier(self, channel=0):
         """Every rank's earlier work on the current stream is complete, and visible
-        to its peers, before any rank's later work starts (stream-ordered)."""
+        to its peers, before any rank's later work starts (stream-ordered).  Barriers
+        issued from two streams at once must use different channels."""
         if self.world > 1:
-            self._hdl.barrier()
+            self._hdl.barrier(channel=channel)
 
-    def _push(self, src, src_row, dst_rank, dst_row, table):
+    def _push(self, src, src_row, dst_rank, dst_row, table, max_ctas=0):
         n_items = int(dst_rank.numel())
         row_bytes = src.shape[1] * src.element_size()
         rc = self._lib.b200gmm_push_rows(
             src.data_ptr(), row_bytes, n_items, 0 if src_row is None else src_row.data_ptr(),
-            dst_rank.data_ptr(), dst_row.data_ptr(), table.data_ptr(),
+            dst_rank.data_ptr(), dst_row.data_ptr(), table.data_ptr(), int(max_ctas),
             torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "b200gmm_push_rows")
 
@@ -326,7 +334,12 @@ class PeerExchange:
         return slots.view(self.num_tokens, self.top_k, self.h_in).sum(1)
 
     def step(self, x, w, grad_rows, gmm_fn):
-        """Same unit of work as ``expert_parallel_step``, over peer memory."""
+        """Same unit of work as ``expert_parallel_step``, over peer memory: four
+        row pushes, each followed by a barrier.  Starts with a barrier, so that
+        whatever an earlier step still reads on any rank is done before this one
+        overwrites the buffers."""
+        self.barrier()
+        self._ahead = None
         a = self.dispatch(x)
         c = gmm_fn(a, w, self.batch_sizes, False, False)
         out_rows = self.combine_rows(c)
@@ -335,53 +348,6 @@ class PeerExchange:
         dw = gmm_fn(a, g, self.batch_sizes, True, False)
         dx = self.combine_reduce(da)
         return out_rows, dx, dw
-
-    def step_overlapped(self, x, w, grad_rows, gmm_fn):
-        """``step`` with the exchanges on a second stream, hidden behind the GEMMs:
-        the gradient dispatch runs under the forward GEMM, the forward combine
-        under dgrad, the dgrad combine under wgrad.  Only the first dispatch and
-        the tail of the last combine stay exposed.  All cross-rank barriers are
-        issued on the exchange stream, in the same order on every rank; a buffer
-        is overwritten only after a barrier that follows every rank's last read.
-        Same results as ``step``."""
-        compute = torch.cuda.current_stream(self.device)
-        comm = self.comm_stream
-        rows = self.local_rows
-        start = compute.record_event()
-        with torch.cuda.stream(comm):
-            comm.wait_event(start)          # previous consumers of the buffers on this rank
-            self.barrier()                  # ... and on every other rank
-            self._push(x, self.item_token, self.item_rank, self.item_row, self._t_a)
-            self.barrier()
-            a_ready = comm.record_event()
-            self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
-            self.barrier()
-            g_ready = comm.record_event()
-        a = self.a_grouped[:rows]
-        g = self.g_grouped[:rows]
-        compute.wait_event(a_ready)
-        c = gmm_fn(a, w, self.batch_sizes, False, False)
-        c_done = compute.record_event()
-        with torch.cuda.stream(comm):
-            comm.wait_event(c_done)
-            self._push(c, None, self.back_rank, self.back_row, self._t_out)
-            self.barrier()
-            c.record_stream(comm)
-        compute.wait_event(g_ready)
-        da = gmm_fn(g, w, self.batch_sizes, False, True)
-        da_done = compute.record_event()
-        with torch.cuda.stream(comm):
-            comm.wait_event(da_done)
-            self._push(da, None, self.back_rank, self.back_row, self._t_da)
-            self.barrier()
-            da.record_stream(comm)
-            slots = self.da_slots[: self.num_tokens * self.top_k]
-            dx = slots.view(self.num_tokens, self.top_k, self.h_in).sum(1)
-            finished = comm.record_event()
-        dw = gmm_fn(a, g, self.batch_sizes, True, False)
-        compute.wait_event(finished)
-        dx.record_stream(compute)
-        return self.out_slots[: self.num_tokens * self.top_k], dx, dw
 
     def _gmm_scatter(self, a, w, dest, trans_b):
         """Local grouped GEMM whose epilogue writes row i to address dest[i]."""
@@ -395,17 +361,74 @@ class PeerExchange:
             torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "b200gmm_run_scatter")
 
-    def step_fused(self, x, w, grad_rows, gmm_fn):
-        """``step`` with both combines fused into the GEMMs: the forward and the
-        dgrad kernels write each result row from their epilogue straight into the
-        token owner's buffer (over NVLink when the owner is another GPU), so only
-        the two dispatches remain as separate passes.  Same results as ``step``."""
+    def step_fused(self, x, w, grad_rows, gmm_fn, x_next=None, overlap=True):
+        """``step`` with the exchange folded into and hidden under the GEMMs.  Same
+        results as ``step``, bit for bit.
+
+        * Both combines are written by the GEMM epilogues: the forward and the dgrad
+          kernels send each result row straight into the token owner's buffer (over
+          NVLink when the owner is another GPU), so no combine pass exists.
+        * The dispatch of the output gradient does not depend on the forward GEMM and
+          runs under it, on a second stream, with a capped number of blocks
+          (``overlap=False``: on the main stream, before the dgrad GEMM).
+        * ``x_next``: the activations of the NEXT call (a training loop knows them:
+          the next micro-batch).  Their dispatch is issued under this step's wgrad
+          GEMM into the second dispatch buffer; the next call, given the same tensor
+          as ``x``, finds its rows in place and starts with the forward GEMM.
+
+        Cross-rank order: a barrier on entry (every rank has finished with the
+        previous step's buffers), one after each dispatch (its rows have arrived),
+        one at the end (the rows the epilogues sent have arrived)."""
+        compute = torch.cuda.current_stream(self.device)
+        comm = self.comm_stream
         pairs = self.num_tokens * self.top_k
-        a = self.dispatch(x)
+        rows = self.local_rows
+        self.barrier()
+        entered = compute.record_event()
+        ahead = self._ahead
+        self._ahead = None
+        if ahead is not None and ahead[0] == x.data_ptr():
+            self._cur = ahead[1]
+            dispatched = ahead[2]
+        else:
+            if ahead is not None:
+                compute.wait_event(ahead[2])   # a dispatch nobody claimed: let it finish before its buffer is reused
+            dispatched = None
+        a_buf, a_table = (self.a_grouped, self._t_a) if self._cur == 0 else (self.a_grouped2, self._t_a2)
+        # gradient rows: under the forward GEMM
+        if overlap:
+            with torch.cuda.stream(comm):
+                comm.wait_event(entered)
+                self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g, self.side_push_ctas)
+                self.barrier(channel=1)
+                g_ready = comm.record_event()
+            grad_rows.record_stream(comm)
+        if dispatched is None:
+            self._push(x, self.item_token, self.item_rank, self.item_row, a_table)
+            self.barrier()
+        else:
+            compute.wait_event(dispatched)
+        a = a_buf[:rows]
         self._gmm_scatter(a, w, self.dest_out, False)
-        g = self.dispatch_rows(grad_rows)      # its barrier also publishes the forward's rows
+        if overlap:
+            compute.wait_event(g_ready)
+        else:
+            self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
+            self.barrier()                     # also publishes the forward's rows
+        g = self.g_grouped[:rows]
         self._gmm_scatter(g, w, self.dest_da, True)
+        if x_next is not None:
+            # next step's activations: under the wgrad GEMM, into the other buffer
+            nxt = 1 - self._cur
+            t_next = self._t_a if nxt == 0 else self._t_a2
+            issued = compute.record_event()
+            with torch.cuda.stream(comm):
+                comm.wait_event(issued)
+                self._push(x_next, self.item_token, self.item_rank, self.item_row, t_next, self.side_push_ctas)
+                self.barrier(channel=1)
+                self._ahead = (x_next.data_ptr(), nxt, comm.record_event())
+            x_next.record_stream(comm)
         dw = gmm_fn(a, g, self.batch_sizes, True, False)
-        self.barrier()                         # dgrad rows have arrived everywhere
+        self.barrier()                         # the rows both epilogues sent have arrived everywhere
         dx = self.da_slots[:pairs].view(self.num_tokens, self.top_k, self.h_in).sum(1)
         return self.out_slots[:pairs], dx, dw

@@ -53,7 +53,7 @@ extern "C" {
 
 /* Number of fields b200gmm_schedule_host / b200gmm_schedule_device write per tile:
  * expert, row0, col0, valid_rows, pipeline stages, kind (0: rows x 256 columns;
- * 1: transposed tile of at most 64 rows x 128 columns). */
+ * 1: transposed tile, all rows of an expert of at most 64 rows x 128 columns). */
 #define B200GMM_SCHEDULE_FIELDS 6
 
 /*
@@ -256,6 +256,27 @@ int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void
                        uint32_t* device_status, void* cuda_stream);
 
 /*
+ * Backward of b200gmm_run_swiglu with respect to its two products, in one
+ * kernel: the gate and up products are recomputed in the accumulator (they were
+ * never stored), and the epilogue reads grad_out (bf16 [tokens, n], the gradient
+ * of c) and writes
+ *   grad_products[0] = grad_out * up * silu'(gate)     silu'(g) = s (1 + g (1 - s)), s = 1 / (1 + exp(-g))
+ *   grad_products[1] = grad_out * silu(gate)
+ * into grad_products (bf16 [2, tokens, n], contiguous): the gradients of the
+ * loss w.r.t. a @ b_gate and a @ b_up.  From them the caller gets the input
+ * gradient with two b200gmm_run calls (trans_b flipped, summed) and the two
+ * weight gradients with two trans_a calls, exactly as for a plain product
+ * (grouped_gemm/ops.py:14-29 of the reference).  Rows past sum(batch_sizes) of
+ * grad_products are left untouched.  The reference has no counterpart.
+ */
+int b200gmm_run_swiglu_backward(const void* a, const void* b_gate, const void* b_up,
+                                const void* grad_out, void* grad_products,
+                                const int64_t* batch_sizes, int batch_sizes_on_device,
+                                int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
+                                void* workspace, size_t workspace_bytes,
+                                uint32_t* device_status, void* cuda_stream);
+
+/*
  * Row exchange for expert parallelism: copy `n_items` rows of `row_bytes` bytes
  * (a multiple of 16) from `src` on this GPU into rows of buffers that may live
  * on other GPUs.  Item i reads row src_row[i] of `src` (row i when src_row is
@@ -265,14 +286,16 @@ int b200gmm_run_swiglu(const void* a, const void* b_gate, const void* b_up, void
  * process (symmetric memory or CUDA IPC) and of this GPU's own buffer at its
  * own rank.  Plain loads and stores only: no TMA, no multicast, and remote
  * memory is only written, never read.  The caller orders the transfer against
- * the consumers on the other GPUs (a barrier after the push).
+ * the consumers on the other GPUs (a barrier after the push).  `max_ctas` > 0
+ * caps the number of thread blocks (default: four per SM), for a transfer that
+ * should run under a GEMM on another stream rather than compete with it.
  * The reference has no counterpart: it is single-GPU and leaves the
  * sort-by-expert permutation to its callers.
  */
 int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items,
                       const int32_t* src_row, const int32_t* dst_rank,
                       const int64_t* dst_row, const void* const* peer_base,
-                      void* cuda_stream);
+                      int max_ctas, void* cuda_stream);
 
 /*
  * Device-side argument fill on its own, for inspection and bit-exact tests:
@@ -291,11 +314,10 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z,
  * __host__ __device__ code as the kernel).  Writes, for every position of the
  * launch order, B200GMM_SCHEDULE_FIELDS int64 values into `out` (at most
  * `max_tiles` tiles) and the tile count into *n_tiles.  CTAs draw positions
- * from a global counter in this order; where tile durations differ widely
- * (trans_a, and the one-CTA variant) the experts are first sorted by their
- * number of rows, largest first (the reference sorts its wgrad problems the
- * same way, csrc/fill_arguments.cuh:80-86), and positions alternate between
- * the front and the back of that order.
+ * from a global counter in this order; for trans_a, where a tile's duration
+ * is its expert's row count, the experts are first sorted by their number of
+ * rows, largest first (the reference sorts its wgrad problems the same way,
+ * csrc/fill_arguments.cuh:80-86), so that the launch ends on short tiles.
  * `cluster_ctas` selects the kernel variant: 1 (each CTA owns 128-row tiles),
  * 2 (a pair of CTAs owns 256-row tiles) or 0 (whatever b200gmm_run would pick
  * for these shapes).  Pure host arithmetic; needs no GPU.  It has no

@@ -143,11 +143,11 @@ def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n, ctas):
         assert starts[e] <= row0 and row0 + valid <= starts[e + 1], "tile leaves its expert's rows"
         if kind:
             assert ctas == 1 and 0 < valid <= 64 and stages == 512 // 128
-            assert row0 + valid == starts[e + 1], "a transposed tile holds an expert's last rows"
+            assert row0 == starts[e] and row0 + valid == starts[e + 1], "a transposed tile holds a whole small expert"
         else:
             assert 0 < valid <= tile_m and stages == 512 // 64
             if ctas == 1:
-                assert valid > 64, "row remainders of at most 64 rows go to transposed tiles"
+                assert sizes[e] > 64, "experts of at most 64 rows go to transposed tiles"
         cover[row0:row0 + valid, col0 // 128:(col0 + width + 127) // 128] += 1
     assert (cover == 1).all()
 
@@ -171,19 +171,18 @@ def test_schedule_wgrad_full_grid_for_every_expert(sizes, ctas):
         assert (cover == 1).all()
 
 
-def test_schedule_order_largest_and_smallest_experts_alternate():
-    """wgrad launch order: experts sorted by rows, largest first; even positions
-    walk that order from the front, odd positions from the back, so the order
-    ends on the mid-sized experts."""
+def test_schedule_order_largest_experts_first_for_wgrad():
+    """wgrad launch order: experts sorted by rows, largest first (ties keep their
+    index order), so that the launch ends on the shortest tiles."""
     sizes = [10, 500, 0, 70, 3000, 200]
     tiles = _schedule(sizes, sum(sizes), 128, 256, 1, 0, 1)     # one tile per expert
-    assert tiles[:, 0].tolist() == [4, 2, 1, 0, 5, 3]
-    # equal sizes keep their index order (stable), whichever end they are taken from
+    assert tiles[:, 0].tolist() == [4, 1, 5, 3, 0, 2]
     tiles = _schedule([64, 64, 64, 64], 256, 128, 256, 1, 0, 1)
-    assert tiles[:, 0].tolist() == [0, 3, 1, 2]
-    # the pair variant of the forward layouts keeps the experts in index order
-    tiles = _schedule([600, 100, 900], 1600, 128, 256, 0, 0, 2)
-    assert (np.diff(tiles[:, 0]) >= 0).all()
+    assert tiles[:, 0].tolist() == [0, 1, 2, 3]
+    # the forward layouts keep the experts in index order
+    for ctas in (1, 2):
+        tiles = _schedule([600, 100, 900], 1600, 128, 256, 0, 0, ctas)
+        assert (np.diff(tiles[:, 0]) >= 0).all()
 
 
 def test_schedule_clamps_rows_past_tokens():

@@ -61,18 +61,18 @@ def test_push_rows_permutation_single_gpu():
     table = torch.tensor([dst.data_ptr()], dtype=torch.int64, device="cuda")
     rank0 = torch.zeros(200, dtype=torch.int32, device="cuda")
     rc = lib.b200gmm_push_rows(src.data_ptr(), 144, 200, src_row.data_ptr(), rank0.data_ptr(),
-                               dst_row.data_ptr(), table.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                               dst_row.data_ptr(), table.data_ptr(), 0, torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     want = torch.zeros_like(dst)
     want[dst_row] = src[src_row.long()]
     assert torch.equal(dst, want)
     # identity source rows, and the argument checks
     rc = lib.b200gmm_push_rows(src.data_ptr(), 144, 50, None, rank0.data_ptr(), dst_row.data_ptr(),
-                               table.data_ptr(), torch.cuda.current_stream().cuda_stream)
+                               table.data_ptr(), 3, torch.cuda.current_stream().cuda_stream)   # three blocks only
     assert rc == 0
     assert torch.equal(dst[dst_row[:50]], src)
     assert lib.b200gmm_push_rows(src.data_ptr(), 100, 50, None, rank0.data_ptr(), dst_row.data_ptr(),
-                                 table.data_ptr(), None) == -1   # rows must be multiples of 16 bytes
+                                 table.data_ptr(), 0, None) == -1   # rows must be multiples of 16 bytes
 
 
 def test_peer_exchange_single_rank_matches_oracle():
@@ -86,12 +86,18 @@ def test_peer_exchange_single_rank_matches_oracle():
     assert torch.equal(back.cpu(), grad)
     out_rows, dx, dw = px.step(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
     out_rows, dx, dw = out_rows.clone(), dx.clone(), dw.clone()
-    o2, dx2, dw2 = px.step_overlapped(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
+    xd, wd, gd = x.cuda(), w.cuda(), grad.cuda()
+    for kwargs in (dict(overlap=False), dict(), dict(x_next=xd), dict(x_next=xd)):
+        # (the last call finds its rows dispatched ahead by the one before)
+        o2, dx2, dw2 = px.step_fused(xd, wd, gd, gmm_fn, **kwargs)
+        torch.cuda.synchronize()
+        assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw), kwargs
+    # rows dispatched ahead for one tensor are not used for another
+    other = (xd.float() * 2).bfloat16()
+    o3, dx3, dw3 = px.step_fused(other, wd, gd, gmm_fn)
+    want3 = px.step(other, wd, gd, gmm_fn)
     torch.cuda.synchronize()
-    assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw)
-    o3, dx3, dw3 = px.step_fused(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
-    torch.cuda.synchronize()
-    assert torch.equal(o3, out_rows) and torch.equal(dx3, dx) and torch.equal(dw3, dw)
+    assert all(torch.equal(u, v) for u, v in zip((o3, dx3, dw3), want3))
     want_rows, want_dx, want_dw = _unsharded_oracle()
     assert _close(out_rows, want_rows) and _close(dx, want_dx, 5e-2) and _close(dw, want_dw, 5e-2)
     assert bool((dw[Z - 1] == 0).all())
@@ -122,15 +128,27 @@ def _worker(rank, world, port, results):
         px = ep.PeerExchange(il, Z, H_IN, H_OUT)
         o2, dx2, dw2 = px.step(xl, wl, gl, gmm_fn)
         o2, dx2, dw2 = o2.clone(), dx2.clone(), dw2.clone()
-        for _ in range(3):   # replayed steps reuse the buffers: the barriers must order them
-            o3, dx3, dw3 = px.step_overlapped(xl, wl, gl, gmm_fn)
-        o3, dx3, dw3 = o3.clone(), dx3.clone(), dw3.clone()
-        for _ in range(3):   # combines fused into the GEMM epilogues (stores into the peer's buffer)
-            o4, dx4, dw4 = px.step_fused(xl, wl, gl, gmm_fn)
-        torch.cuda.synchronize()
-        same = bool(torch.equal(o1, o2) and torch.equal(dw1, dw2) and torch.equal(dx1, dx2)
-                    and torch.equal(o3, o2) and torch.equal(dw3, dw2) and torch.equal(dx3, dx2)
-                    and torch.equal(o4, o2) and torch.equal(dw4, dw2) and torch.equal(dx4, dx2))
+        same = bool(torch.equal(o1, o2) and torch.equal(dw1, dw2) and torch.equal(dx1, dx2))
+        # Replayed steps reuse the buffers, so the barriers must order them: every
+        # iteration gets its own inputs and is compared with its own all-to-all
+        # result (an overwrite by a rank that runs ahead would change the output).
+        # Iteration i announces the activations of iteration i + 1.
+        xs = [(xl.float() * (1 + 0.25 * i)).bfloat16() for i in range(5)]
+        gs = [(gl.float() * (1 - 0.125 * i)).bfloat16() for i in range(5)]
+        for mode in ("pushes", "fused", "fused-no-overlap", "fused-ahead"):
+            for i in range(4):
+                want = ep.expert_parallel_step(xs[i], wl, gs[i], plan, gmm_fn)
+                if mode == "pushes":
+                    got = px.step(xs[i], wl, gs[i], gmm_fn)
+                elif mode == "fused":
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn)
+                elif mode == "fused-no-overlap":
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, overlap=False)
+                else:
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, x_next=xs[i + 1])
+                got = [t.clone() for t in got]
+                torch.cuda.synchronize()
+                same = same and all(torch.equal(u, v) for u, v in zip(got, want))
         results[rank] = (same, o2.cpu(), dx2.float().cpu(), dw2.cpu(), backend.device_status(dev))
     finally:
         dist.destroy_process_group()

@@ -755,3 +755,47 @@ def test_gmm_scatter_row_index_out_of_range_is_skipped_and_flagged(gg, sizes, ac
         keep[bad_rows] = False
         assert torch.equal(out[idx[keep]], good[idx[keep]])
         assert bool((out[idx[bad_rows]] == 0).all())
+
+
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("sizes,k,n", [
+    ([128, 128, 128, 128], 128, 128),
+    ([300, 0, 5, 700, 129, 64, 1, 513], 200, 328),
+    ([2000, 24], 512, 72),
+])
+def test_fused_gmm_swiglu_autograd(gg, trans_b, sizes, k, n):
+    """fused.gmm_swiglu forward and backward against torch.autograd on the fp32
+    composition of the oracle's per-expert loop (ops.py:14-29's contract, twice)."""
+    from grouped_gemm_b200 import fused
+    torch.manual_seed(31)
+    T, z = sum(sizes), len(sizes)
+    a_cpu = torch.randn(T, k).bfloat16()
+    shape = (z, n, k) if trans_b else (z, k, n)
+    wg_cpu = (torch.randn(*shape) * 0.1).bfloat16()
+    wu_cpu = (torch.randn(*shape) * 0.1).bfloat16()
+    dh_cpu = torch.randn(T, n).bfloat16()
+    bs_cpu = torch.tensor(sizes, dtype=torch.int64)
+    # fp32 reference with autograd
+    a32, wg32, wu32 = (t.float().requires_grad_(True) for t in (a_cpu, wg_cpu, wu_cpu))
+    outs, start = [], 0
+    for i, size in enumerate(sizes):
+        rows = a32[start:start + size]
+        g = rows @ (wg32[i].t() if trans_b else wg32[i])
+        u = rows @ (wu32[i].t() if trans_b else wu32[i])
+        outs.append(torch.nn.functional.silu(g) * u)
+        start += size
+    ref = torch.cat(outs)
+    ref.backward(dh_cpu.float())
+    a = a_cpu.cuda().requires_grad_(True)
+    wg = wg_cpu.cuda().requires_grad_(True)
+    wu = wu_cpu.cuda().requires_grad_(True)
+    out = fused.gmm_swiglu(a, wg, wu, bs_cpu.cuda(), trans_b)
+    util.assert_close(out, ref.detach(), what="gated forward")
+    out.backward(dh_cpu.cuda())
+    # gradients are sums over up to 2000 rows / 328 columns of bf16-rounded terms:
+    # tolerance relative to the size of the gradient tensor, as for the plain backward
+    for got, want, name in ((a.grad, a32.grad, "a.grad"), (wg.grad, wg32.grad, "b_gate.grad"), (wu.grad, wu32.grad, "b_up.grad")):
+        scale = float(want.abs().max()) + 1e-6
+        err = (got.float().cpu() - want).abs()
+        assert bool((err <= 2e-2 * scale + 1e-2 * want.abs()).all()), f"{name}: max err {float(err.max()):.4g} (scale {scale:.4g})"
+    assert bool((wg.grad[[i for i, s_ in enumerate(sizes) if s_ == 0]] == 0).all())
