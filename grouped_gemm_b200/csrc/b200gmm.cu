@@ -200,21 +200,23 @@ int64_t env_int64(const char* name, int64_t fallback) {
   return (v != nullptr && *v != '\0') ? std::atoll(v) : fallback;
 }
 
-// bf16 tensor map (128-byte swizzle unless told otherwise); dims/box innermost first.
+// bf16 tensor map (128-byte swizzle unless told otherwise); dims/box innermost first,
+// strides in bytes for dimensions 1 .. rank-1 (nullptr: packed).
 int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-               const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
+               const uint32_t* box, CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B,
+               const uint64_t* strides = nullptr) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return B200GMM_ECUDA;
-  cuuint64_t gdim[3];
-  cuuint64_t gstride[2];
-  cuuint32_t gbox[3];
-  cuuint32_t estride[3] = {1, 1, 1};
+  cuuint64_t gdim[4];
+  cuuint64_t gstride[3];
+  cuuint32_t gbox[4];
+  cuuint32_t estride[4] = {1, 1, 1, 1};
   uint64_t stride = 2;
   for (int i = 0; i < rank; ++i) {
     gdim[i] = dims[i];
     gbox[i] = box[i];
     stride *= dims[i];
-    if (i + 1 < rank) gstride[i] = stride;
+    if (i + 1 < rank) gstride[i] = strides != nullptr ? strides[i] : stride;
   }
   const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank),
                         const_cast<void*>(base), gdim, gstride, gbox, estride,
@@ -226,6 +228,18 @@ int encode_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dim
                  (unsigned long long)(rank > 2 ? gdim[2] : 0), gbox[0], gbox[1], rank > 2 ? gbox[2] : 0u);
   }
   return r == CUDA_SUCCESS ? B200GMM_OK : B200GMM_ETENSORMAP;
+}
+
+// A row-major [.., rows, cols] operand whose tiles are staged as boxes of 64 columns
+// (MN-major for the tensor core): seen as {64, rows, cols / 64 (, experts)}, one TMA
+// load brings `boxes` neighbouring 64-column boxes, which land one after the other
+// in shared memory exactly as separate loads would put them.  cols % 64 == 0.
+int encode_blocked(CUtensorMap* map, const void* base, uint64_t cols, uint64_t rows, uint64_t experts,
+                   uint32_t box_rows, uint32_t boxes) {
+  const uint64_t dims[4] = {64, rows, cols / 64, experts};
+  const uint64_t strides[3] = {cols * 2, 128, rows * cols * 2};
+  const uint32_t box[4] = {64, box_rows, boxes, 1};
+  return encode_map(map, base, experts > 0 ? 4 : 3, dims, box, CU_TENSOR_MAP_SWIZZLE_128B, strides);
 }
 
 // Which variant a problem runs on.  Only shapes known on the host may decide
@@ -260,6 +274,9 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   p->n = n;
   if (ctas != 1 && ctas != 2) return B200GMM_EINVAL;
   p->tile_m = kBlockM * ctas;
+  derive(p);
+  p->wide_a = 0;
+  p->wide_b = 0;
   p->group_m = env_int("B200GMM_GROUP_M", ctas == 2 ? 8 : 16);
   if (p->group_m < 1) p->group_m = 1;
   // Tiles are drawn from a global counter.  For wgrad, where a tile's duration is
@@ -267,7 +284,11 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   // CTAs that finish early find short tiles left.
   p->dynamic = env_int("B200GMM_DYNAMIC", 1) != 0;
   p->order = (p->dynamic && z > 1 && p->mode == kTN) ? env_int("B200GMM_ORDER", 1) : 0;
-  p->light = (p->mode != kTN && ctas == 1 && !f.gather && !f.swiglu) ? env_int("B200GMM_LIGHT", 1) : 0;
+  // Transposed tiles for experts of at most 64 rows: off unless asked for.  They
+  // take 4x fewer tensor-core cycles on such experts, but those experts are bound
+  // by streaming their weights from HBM either way, and measured end to end the
+  // launch was not faster with them (B200GMM_LIGHT=1 switches them on).
+  p->light = (p->mode != kTN && ctas == 1 && !f.gather && !f.swiglu) ? env_int("B200GMM_LIGHT", 0) : 0;
   const int64_t wait_ns = env_int64("B200GMM_WAIT_LIMIT_NS", static_cast<int64_t>(ptx::kWaitLimitNs));
   p->wait_ns = wait_ns > 0 ? wait_ns : static_cast<int64_t>(ptx::kWaitLimitNs);
   // Upper bound on the tile count must fit the kernel's 32-bit tile index (twice:
@@ -443,6 +464,8 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     const uint32_t ba[2] = {kBlockK, uint32_t(kBlockM)};
     const uint64_t db[3] = {N, D1, Z};
     const uint32_t bb[3] = {64, kBlockK, 1};
+    // (One load per 64-column box: a single load of all the boxes of a stage through
+    // a {64, k, n / 64, z} view of b measured 10-15 % slower in this layout.)
     if ((rc = encode_map(&map_b, b, 3, db, bb)) != 0) return rc;
     if (swiglu && (rc = encode_map(&map_b2, b2, 3, db, bb)) != 0) return rc;
     if (gather) map_a = map_b;
@@ -472,9 +495,16 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     const uint64_t da[2] = {D1, T};
     const uint64_t db[2] = {N, T};
     const uint32_t bx[2] = {64, kBlockK};
-    if ((rc = encode_map(&map_b, b, 2, db, bx)) != 0) return rc;
+    // wgrad: both operands are staged as 64-column boxes; where the column count
+    // allows, one load brings all boxes of a stage (half the TMA instructions).
+    p.wide_b = (N % 64 == 0) ? 1 : 0;
+    p.wide_a = (D1 % 64 == 0 && !gather) ? 1 : 0;
+    if (p.wide_b) rc = encode_blocked(&map_b, b, N, T, 0, kBlockK, kBlockN / ctas / 64);
+    else rc = encode_map(&map_b, b, 2, db, bx);
+    if (rc != 0) return rc;
     if (gather) map_a = map_b;
-    else if ((rc = encode_map(&map_a, a, 2, da, bx)) != 0) return rc;
+    else if ((rc = p.wide_a ? encode_blocked(&map_a, a, D1, T, 0, kBlockK, kBlockM / 64)
+                            : encode_map(&map_a, a, 2, da, bx)) != 0) return rc;
   }
 
   if (!have_b2) map_b2 = map_b;  // unused by the kernel, but a valid map
@@ -679,6 +709,7 @@ int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a
   p.n = n;
   p.tile_m = kBlockM;
   p.group_m = 1;
+  derive(&p);
   fill_offsets_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(batch_sizes_device, p,
                                                                             out_device);
   if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;

@@ -257,21 +257,27 @@ struct TileFeed {
   ptx::WaitCtx wait;
   uint32_t taken;   // positions taken (or published) so far
   int map;          // sched_map entry of the position taken last
+  bool remote;      // this role sits in the peer CTA: what it reads was written from the leader
 
-  __device__ TileFeed(SmemTail* tail_, const ptx::WaitCtx& w) : tail(tail_), wait(w), taken(0), map(0) {}
+  __device__ TileFeed(SmemTail* tail_, const ptx::WaitCtx& w, bool in_peer = false)
+      : tail(tail_), wait(w), taken(0), map(0), remote(in_peer) {}
 
   // Consumer side, called by every lane of a warp (warp_wide) or by one thread.
   __device__ __forceinline__ int take(bool warp_wide, int lane) {
     const uint32_t slot = taken % kSchedSlots;
     const uint32_t parity = (taken / kSchedSlots) & 1u;
     ++taken;
-    if (!ptx::mbar_wait<kPair, 32>(ptx::smem_u32(&tail->sched_full[slot]), parity, wait)) return kNoTile;
+    const uint32_t full = ptx::smem_u32(&tail->sched_full[slot]);
+    const bool got = (kPair && remote) ? ptx::mbar_wait<true, 32>(full, parity, wait)
+                                       : ptx::mbar_wait<false, 32>(full, parity, wait);
+    if (!got) return kNoTile;
     const int t = *reinterpret_cast<volatile int*>(&tail->sched_tile[slot]);
     map = *reinterpret_cast<volatile int*>(&tail->sched_map[slot]);
     if (warp_wide) __syncwarp();
     if (!warp_wide || lane == 0) {
+      // Both values are in registers: the slot may be overwritten from here on.
       const uint32_t bar = ptx::smem_u32(&tail->sched_empty[slot]);
-      if (kPair) ptx::mbar_arrive_release_cluster(ptx::mapa(bar, 0));
+      if (kPair) ptx::mbar_arrive_cluster(ptx::mapa(bar, 0));
       else ptx::mbar_arrive(bar);
     }
     return t;
@@ -397,7 +403,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     // ---------------------------------------------------------- TMA producer
     if (lane == 0) {
       TileWalker walk(p, tail);
-      TileFeed<kPair> feed(tail, wait);
+      TileFeed<kPair> feed(tail, wait, !leader);
       Tile t;
       uint32_t s = 0, ph = 0;
       bool ok = true;
@@ -477,12 +483,22 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               }
             } else {
               const int r0 = t.k_row0 + k0;
+              if (!GATHER) {
+                if (p.wide_a) {
+                  ptx::tma_load_3d(sa, tn_a, local_bar, 0, r0, t.row0 >> 6);
+                } else {
 #pragma unroll
-              for (int j = 0; j < kBlockM / 64; ++j)
-                if (!GATHER) ptx::tma_load_2d(sa + j * kBoxBytes, tn_a, local_bar, t.row0 + j * 64, r0);
+                  for (int j = 0; j < kBlockM / 64; ++j)
+                    ptx::tma_load_2d(sa + j * kBoxBytes, tn_a, local_bar, t.row0 + j * 64, r0);
+                }
+              }
+              if (p.wide_b) {
+                ptx::tma_load_3d(sb, tn_b, local_bar, 0, r0, t.col0 >> 6);
+              } else {
 #pragma unroll
-              for (int j = 0; j < G::kBCols / 64; ++j)
-                ptx::tma_load_2d(sb + j * kBoxBytes, tn_b, local_bar, t.col0 + j * 64, r0);
+                for (int j = 0; j < G::kBCols / 64; ++j)
+                  ptx::tma_load_2d(sb + j * kBoxBytes, tn_b, local_bar, t.col0 + j * 64, r0);
+              }
             }
           } else {
             // Pair: this CTA stages rows [row0+row_off, +128) of A and columns
@@ -506,12 +522,22 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
               else ptx::tma_load_3d_pair(sb, &map_b, bar, k0, t.col0 + col_off, t.expert);
             } else {
               const int r0 = t.k_row0 + k0;
+              if (!GATHER) {
+                if (p.wide_a) {
+                  ptx::tma_load_3d_pair(sa, tn_a, bar, 0, r0, (t.row0 + row_off) >> 6);
+                } else {
 #pragma unroll
-              for (int j = 0; j < kBlockM / 64; ++j)
-                if (!GATHER) ptx::tma_load_2d_pair(sa + j * kBoxBytes, tn_a, bar, t.row0 + row_off + j * 64, r0);
+                  for (int j = 0; j < kBlockM / 64; ++j)
+                    ptx::tma_load_2d_pair(sa + j * kBoxBytes, tn_a, bar, t.row0 + row_off + j * 64, r0);
+                }
+              }
+              if (p.wide_b) {
+                ptx::tma_load_3d_pair(sb, tn_b, bar, 0, r0, (t.col0 + col_off) >> 6);
+              } else {
 #pragma unroll
-              for (int j = 0; j < G::kBCols / 64; ++j)
-                ptx::tma_load_2d_pair(sb + j * kBoxBytes, tn_b, bar, t.col0 + col_off + j * 64, r0);
+                for (int j = 0; j < G::kBCols / 64; ++j)
+                  ptx::tma_load_2d_pair(sb + j * kBoxBytes, tn_b, bar, t.col0 + col_off + j * 64, r0);
+              }
             }
           }
           if (++s == kStages) { s = 0; ph ^= 1u; }
@@ -522,7 +548,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
   } else if (warp == 1 && leader) {
     // ---------------------------------------------------------- MMA issuer
     TileWalker walk(p, tail);
-    TileFeed<kPair> feed(tail, wait);
+    TileFeed<kPair> feed(tail, wait, !leader);
     Tile t;
     uint32_t s = 0, ph = 0, it = 0;
     bool ok = true;
@@ -629,7 +655,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       if (lane == 0) {
         TileWalker walk(p, tail);
-        TileFeed<kPair> feed(tail, wait);
+        TileFeed<kPair> feed(tail, wait, !leader);
         Tile t;
         // wgrad: the map slot clipped to the current expert, and for every slot the
         // index (in this cluster's sequence of tiles) of the last tile that loads
@@ -709,7 +735,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const uint32_t full_bar = kPair ? ptx::mapa(ptx::smem_u32(&tail->full[w]), 0) : ptx::smem_u32(&tail->full[w]);
     const uint32_t empty_bar = ptx::smem_u32(&tail->empty[w]);
     TileWalker walk(p, tail);
-    TileFeed<kPair> feed(tail, wait);
+    TileFeed<kPair> feed(tail, wait, !leader);
     Tile t;
     uint32_t ph = 0;  // parity of this stage's current use
     int next = w;     // position in the stream of k-blocks of this warp's next one
@@ -825,7 +851,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     const int col_base = half * (kBlockN / 2);
     const uint32_t my_out = out_base + uint32_t(warp - 2) * (G::kOutBufBytes * G::kOutBufs);
     TileWalker walk(p, tail);
-    TileFeed<kPair> feed(tail, wait);
+    TileFeed<kPair> feed(tail, wait, !leader);
     Tile t;
     uint32_t it = 0;
     uint32_t stores = 0;  // TMA stores this warp has issued (lane 0's bulk groups)

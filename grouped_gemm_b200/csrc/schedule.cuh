@@ -52,7 +52,20 @@ struct Problem {
   int order;       // 0: experts in index order.  1: experts sorted by rows, largest first
   int dynamic;     // 1: CTAs draw positions of the launch order from a global counter
   int64_t wait_ns; // limit of every wait inside the kernel, in nanoseconds
+  // Derived on the host so that decoding a tile needs no 64-bit division:
+  int nt;          // column tiles of kBlockN: ceil(n / 256)
+  int mt;          // TN: row tiles of c[i]: ceil(d1 / tile_m)
+  int lt;          // column tiles of a transposed tile's width: ceil(n / 128)
+  int wide_a;      // TN: a's columns are a multiple of 64, one TMA load brings all 64-column boxes of a stage
+  int wide_b;      // TN: same for b
 };
+
+// Fills the derived fields of a Problem whose shape fields are set.
+B200GMM_HD void derive(Problem* p) {
+  p->nt = static_cast<int>((p->n + kBlockN - 1) / kBlockN);
+  p->mt = static_cast<int>((p->d1 + p->tile_m - 1) / p->tile_m);
+  p->lt = static_cast<int>((p->n + kLightCols - 1) / kLightCols);
+}
 
 struct Tile {
   int expert;
@@ -64,26 +77,23 @@ struct Tile {
   int kind;        // 0: tile_m x 256 tile; 1: transposed tile (valid_rows <= kLightRows, kLightCols columns)
 };
 
-B200GMM_HD int ceil_div_i(int64_t a, int64_t b) { return static_cast<int>((a + b - 1) / b); }
-
-B200GMM_HD int col_tiles(const Problem& p) { return ceil_div_i(p.n, kBlockN); }
+B200GMM_HD int ceil_div_i(int a, int b) { return (a + b - 1) / b; }
 
 // Row-tiles of tile_m rows an expert with `rows` rows gets, and the rows that go
 // to transposed tiles instead (0 if none).
-B200GMM_HD int heavy_row_tiles(const Problem& p, int64_t rows) {
+B200GMM_HD int heavy_row_tiles(const Problem& p, int rows) {
   if (p.light && rows <= kLightRows) return 0;
   return ceil_div_i(rows, p.tile_m);
 }
-B200GMM_HD int light_rows(const Problem& p, int64_t rows) {
-  return (p.light && rows <= kLightRows) ? static_cast<int>(rows) : 0;
+B200GMM_HD int light_rows(const Problem& p, int rows) {
+  return (p.light && rows <= kLightRows) ? rows : 0;
 }
 
 // Tiles of one expert.  TN always has the full c[i] grid (empty experts still
 // need their zeros written, csrc/fill_arguments.cuh:100-119).
-B200GMM_HD int expert_tiles(const Problem& p, int64_t rows) {
-  const int nt = col_tiles(p);
-  if (p.mode == kTN) return ceil_div_i(p.d1, p.tile_m) * nt;
-  return heavy_row_tiles(p, rows) * nt + (light_rows(p, rows) > 0 ? ceil_div_i(p.n, kLightCols) : 0);
+B200GMM_HD int expert_tiles(const Problem& p, int rows) {
+  if (p.mode == kTN) return p.mt * p.nt;
+  return heavy_row_tiles(p, rows) * p.nt + (light_rows(p, rows) > 0 ? p.lt : 0);
 }
 
 // Pipeline stages (ring slots) one tile consumes.
@@ -109,11 +119,10 @@ B200GMM_HD Tile make_tile(const Problem& p, int expert, int local, int rs, int r
   Tile t;
   t.expert = expert;
   t.kind = 0;
-  const int nt = col_tiles(p);
+  const int nt = p.nt;
   int mi, ni;
   if (p.mode == kTN) {
-    const int mt = ceil_div_i(p.d1, p.tile_m);
-    decode_in_expert(local, mt, nt, p.group_m, &mi, &ni);
+    decode_in_expert(local, p.mt, nt, p.group_m, &mi, &ni);
     t.row0 = mi * p.tile_m;
     const int left = static_cast<int>(p.d1) - t.row0;
     t.valid_rows = left < p.tile_m ? left : p.tile_m;

@@ -129,9 +129,12 @@ SIZE_SETS = [
 @pytest.mark.parametrize("trans_b", [0, 1])
 @pytest.mark.parametrize("n", [128, 256, 328, 1536])
 @pytest.mark.parametrize("ctas", [1, 2])
-def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n, ctas):
+@pytest.mark.parametrize("light", ["0", "1"])
+def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n, ctas, light, monkeypatch):
     """Every output element belongs to exactly one tile: 128-column granularity,
-    since the transposed tiles of the one-CTA variant are 128 columns wide."""
+    since the transposed tiles of the one-CTA variant (B200GMM_LIGHT=1) are 128
+    columns wide."""
+    monkeypatch.setenv("B200GMM_LIGHT", light)
     tokens = sum(sizes)
     tile_m = 128 * ctas
     tiles = _schedule(sizes, tokens, 512, n, 0, trans_b, ctas)
@@ -142,11 +145,11 @@ def test_schedule_covers_rows_and_columns_once(sizes, trans_b, n, ctas):
         assert col0 % width == 0 and col0 < n
         assert starts[e] <= row0 and row0 + valid <= starts[e + 1], "tile leaves its expert's rows"
         if kind:
-            assert ctas == 1 and 0 < valid <= 64 and stages == 512 // 128
+            assert light == "1" and ctas == 1 and 0 < valid <= 64 and stages == 512 // 128
             assert row0 == starts[e] and row0 + valid == starts[e + 1], "a transposed tile holds a whole small expert"
         else:
             assert 0 < valid <= tile_m and stages == 512 // 64
-            if ctas == 1:
+            if ctas == 1 and light == "1":
                 assert sizes[e] > 64, "experts of at most 64 rows go to transposed tiles"
         cover[row0:row0 + valid, col0 // 128:(col0 + width + 127) // 128] += 1
     assert (cover == 1).all()
@@ -192,9 +195,10 @@ def test_schedule_clamps_rows_past_tokens():
         assert int((tiles[:, 1] + tiles[:, 3]).max()) <= 150
 
 
-def test_variant_choice_depends_on_shapes_only():
+def test_variant_choice_depends_on_shapes_only(monkeypatch):
     """cluster_ctas=0 asks for the variant b200gmm_run would use: pairs for
     experts with many rows, single CTAs for fine-grained groups."""
+    monkeypatch.setenv("B200GMM_LIGHT", "1")
     big = _schedule([4096] * 8, 32768, 512, 512, 0, 0, 0)
     small = _schedule([64] * 64, 4096, 512, 512, 0, 0, 0)
     assert int(big[:, 3].max()) == 256 and int(small[:, 3].max()) == 64

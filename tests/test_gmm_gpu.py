@@ -25,14 +25,19 @@ def gg():
     return grouped_gemm_b200
 
 
-@pytest.fixture(autouse=True, params=["1", "2", "auto"], ids=["one-cta", "cta-pair", "auto"])
+@pytest.fixture(autouse=True, params=["1", "1-light", "2", "auto"],
+                ids=["one-cta", "one-cta-transposed-tiles", "cta-pair", "auto"])
 def _variant(request, monkeypatch, gg):
-    """Every test runs on both kernel variants: tiles owned by one CTA, and tiles
-    owned by a pair of CTAs (tcgen05 cta_group::2), and once with the library's
-    own choice of variant.  The
-    library reads the variable on each call."""
+    """Every test runs on both kernel variants: tiles owned by one CTA (once more
+    with experts of at most 64 rows as transposed tiles), and tiles owned by a
+    pair of CTAs (tcgen05 cta_group::2), and once with the library's own choice of
+    variant.  The library reads the variables on each call."""
+    monkeypatch.delenv("B200GMM_LIGHT", raising=False)
     if request.param == "auto":
         monkeypatch.delenv("B200GMM_CTAS", raising=False)
+    elif request.param == "1-light":
+        monkeypatch.setenv("B200GMM_CTAS", "1")
+        monkeypatch.setenv("B200GMM_LIGHT", "1")
     else:
         monkeypatch.setenv("B200GMM_CTAS", request.param)
     yield request.param

@@ -61,8 +61,9 @@ def _cases():
 
 @pytest.mark.parametrize("case", sorted(_cases()))
 @pytest.mark.parametrize("mode", ["nn", "nt", "tn"])
-@pytest.mark.parametrize("ctas", [1, 2])
-def test_device_schedule_equals_host_replay(case, mode, ctas):
+@pytest.mark.parametrize("ctas,light", [(1, "0"), (1, "1"), (2, "0")])
+def test_device_schedule_equals_host_replay(case, mode, ctas, light, monkeypatch):
+    monkeypatch.setenv("B200GMM_LIGHT", light)
     sizes, d1, n = _cases()[case]
     tokens = sum(sizes)
     ta, tb = int(mode == "tn"), int(mode == "nt")
