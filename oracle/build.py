@@ -1,4 +1,10 @@
-"""Compile oracle/fill_oracle.c into oracle/libgmm_oracle.so (gcc)."""
+"""Compile oracle/fill_oracle.c into oracle/libgmm_oracle.so (gcc): the C
+restatement of the argument fill that the tests check the CUDA path against.
+
+There is no oracle/_ref target: the reference's own native code cannot be
+compiled without its CUTLASS submodule (both of its sources include CUTLASS
+headers, and the submodule is empty in a plain checkout), and it has no CPU path.
+"""
 import os
 import subprocess
 

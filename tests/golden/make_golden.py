@@ -28,15 +28,39 @@ import torch
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "ops_test_golden.npz")
 
-# (z, m, k, n, variable-size settings).  The first three shapes are from the
-# reference grid; the z=4 shape is a smaller one of the same family.  Kept to
-# the small end so the fixture stays well under 1 MB.
+# (z, m, k, n, variable-size settings): the reference's whole grid
+# (ops_test.py:29-36) with fixed and variable sizes, plus a smaller shape of the
+# same family.  Results of more than MAX_ELEMS elements are stored as a regular
+# sample (every sr-th row, every sc-th column of the tensor seen as 2-D), the steps
+# beside them, so that the fixture stays around 1 MB.
 CASES = [
     (1, 128, 128, 128, (False, True)),
-    (1, 128, 256, 512, (False,)),
+    (8, 128, 128, 128, (False, True)),
+    (16, 128, 128, 128, (False, True)),
+    (1, 128, 256, 512, (False, True)),
+    (8, 128, 256, 512, (False, True)),
+    (16, 128, 256, 512, (False, True)),
     (4, 64, 128, 128, (False, True)),
-    (8, 128, 128, 128, (True,)),
 ]
+MAX_ELEMS = 8192
+
+
+def sample_steps(rows, cols):
+    """Row and column steps that bring rows x cols down to about MAX_ELEMS; odd, so
+    that the sample does not lock onto tile boundaries."""
+    sr = sc = 1
+    while (rows // sr + 1) * (cols // sc + 1) > MAX_ELEMS:
+        if rows // sr >= cols // sc:
+            sr += 2
+        else:
+            sc += 2
+    return sr, sc
+
+
+def sampled(t):
+    t2 = t.detach().reshape(-1, t.shape[-1])
+    sr, sc = sample_steps(t2.shape[0], t2.shape[1])
+    return bits(t2[::sr, ::sc]), np.array([sr, sc], dtype=np.int64)
 
 
 def load_reference_functions(ref_root):
@@ -82,9 +106,8 @@ def main():
                     expected.sum().backward()
                     key = f"z{z}_m{m}_k{k}_n{n}_tb{int(trans_b)}_var{int(variable)}"
                     out[key + "/batch_sizes"] = bs.numpy().astype(np.int64)
-                    out[key + "/out"] = bits(expected)
-                    out[key + "/a_grad"] = bits(a.grad)
-                    out[key + "/b_grad"] = bits(b.grad)
+                    for name, t in (("out", expected), ("a_grad", a.grad), ("b_grad", b.grad)):
+                        out[key + "/" + name], out[key + "/" + name + "_step"] = sampled(t)
                     # inputs are regenerated from the seed by the tests; the digest
                     # detects a generator that drifted
                     h = hashlib.sha256(bits(a).tobytes() + bits(b).tobytes()).hexdigest()

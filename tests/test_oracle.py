@@ -27,17 +27,18 @@ def test_oracle_matches_reference_golden(key):
     assert util.input_digest(a, b) == digest, "seeded inputs differ from the ones the golden was made with"
     bs = torch.from_numpy(_DATA[key + "/batch_sizes"])
     out = gmm_oracle.gmm(a, b, bs, trans_b=trans_b)
-    gold = util.from_bits(_DATA[key + "/out"])
+    gold, out_s = util.golden_pair(_DATA, key, "out", out)
     # The golden is the reference loop in bf16 on CPU; this oracle upcasts to
     # fp32 first.  Both accumulate in fp32 and round once, so they agree to the
     # last bit except where summation order flips a rounding.
-    assert gmm_oracle.reference_allclose_pct(out, gold) <= 2.0
-    util.assert_close(out, gold, rtol=1e-2, atol=1e-6, what="forward")
+    assert gmm_oracle.reference_allclose_pct(out_s, gold) <= 2.0
+    util.assert_close(out_s, gold, rtol=1e-2, atol=1e-6, what="forward")
     # gradients of out.sum(): upstream gradient of ones (ops_test.py:77-80)
-    grad = torch.ones_like(gold)
+    grad = torch.ones_like(out)
     agrad, bgrad = gmm_oracle.gmm_backward(a, b, bs, grad, trans_b=trans_b)
-    util.assert_close(agrad, util.from_bits(_DATA[key + "/a_grad"]), rtol=1e-2, atol=1e-6, what="a.grad")
-    util.assert_close(bgrad, util.from_bits(_DATA[key + "/b_grad"]), rtol=1e-2, atol=1e-6, what="b.grad")
+    for got, name in ((agrad, "a_grad"), (bgrad, "b_grad")):
+        gold, got_s = util.golden_pair(_DATA, key, name, got)
+        util.assert_close(got_s, gold, rtol=1e-2, atol=1e-6, what=name)
 
 
 def test_oracle_zero_k_known_answer():

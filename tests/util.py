@@ -50,6 +50,16 @@ def golden_cases():
     return data, keys
 
 
+def golden_pair(data, key, name, tensor):
+    """(golden values, the same elements of ``tensor``): large results are stored
+    as a regular sample of the tensor seen as 2-D (steps in ``<name>_step``)."""
+    sr, sc = (int(v) for v in data[key + "/" + name + "_step"])
+    gold = from_bits(data[key + "/" + name])
+    got = tensor.detach().reshape(-1, tensor.shape[-1])[::sr, ::sc]
+    assert tuple(got.shape) == tuple(gold.shape), f"{name}: sample shape {tuple(got.shape)} != {tuple(gold.shape)}"
+    return gold, got
+
+
 def parse_key(key):
     parts = dict((p[0] if p[0] in "zmkn" else p[:-1], p) for p in key.split("_"))
     z = int(parts["z"][1:]); m = int(parts["m"][1:]); k = int(parts["k"][1:]); n = int(parts["n"][1:])
