@@ -733,7 +733,7 @@ def ep_value_single(steps, dev):
     grad = torch.randn(EP["tokens"] * EP["top_k"], EP["ffn"], device=dev, generator=g).bfloat16()
     px = ep.PeerExchange(ids, EP["z"], EP["hidden"], EP["ffn"], single_rank=True)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
-    step = lambda: px.step_fused(x, w, grad, gmm_fn, x_next=x)
+    step = lambda: px.step_fused(x, w, grad, gmm_fn)
     for _ in range(3):
         step()
     steps = max(steps, 2)
@@ -752,8 +752,8 @@ def ep_parity(ep, px, plan, x, w, grad, gmm_fn, backend, rank):
     local GEMMs of this rank against an fp32 CPU product on sampled rows."""
     want = ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
     differs = []
-    for tag, kwargs in (("step_fused", dict(x_next=x)), ("step_fused with rows dispatched ahead", dict(x_next=x))):
-        got = px.step_fused(x, w, grad, gmm_fn, **kwargs)
+    for tag in ("step_fused", "step_fused again (buffers reused)"):
+        got = px.step_fused(x, w, grad, gmm_fn)
         torch.cuda.synchronize()
         for name, u, v in zip(("out_rows", "dx", "dw"), got, want):
             if u.shape != v.shape or not torch.equal(u, v):
@@ -852,11 +852,8 @@ def measure_multi(args):
             parity = ep_parity(ep, px, plan, x, w, grad, gmm_fn, backend, rank)
         if args.no_fused_combine:
             step = lambda: px.step(x, w, grad, gmm_fn)
-        elif args.no_overlap:
-            step = lambda: px.step_fused(x, w, grad, gmm_fn, overlap=False)
         else:
-            # x_next: the next step's activations are dispatched under this step's wgrad
-            step = lambda: px.step_fused(x, w, grad, gmm_fn, x_next=x)
+            step = lambda: px.step_fused(x, w, grad, gmm_fn)
         exchange_step = step
     else:
         step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
@@ -871,6 +868,12 @@ def measure_multi(args):
     launches = (_capi.launch_count() - launches0) * world // args.rounds
     ms_step = sorted(round_ms)[len(round_ms) // 2]
     value = ep_flops() / ms_step / 1e9
+
+    # where a step's time goes on this rank's main stream (one more step, marked with events)
+    phases = None
+    if px is not None and not (args.no_fused_combine):
+        px.step_fused(x, w, grad, gmm_fn, timeline=True)
+        phases = px.phase_times()
 
     # the same step with NCCL all-to-all as the exchange (the baseline of this path)
     nccl_exchange = None
@@ -943,12 +946,10 @@ def measure_multi(args):
                           + ("4 row pushes per step" if args.no_fused_combine else
                              "2 row pushes (dispatch) per step, both combines written by the GEMM epilogues "
                              "straight into the token owners' buffers")
-                          + ("" if (args.no_fused_combine or args.no_overlap) else
-                             "; the gradient dispatch runs under the forward GEMM and the next step's activation "
-                             "dispatch under this step's wgrad GEMM, on a second stream"))
+                          )
                          if args.exchange == "peer" else "NCCL all_to_all_single + index gathers" + exchange_note),
             "rounds": {"count": args.rounds, "ms_per_step_min": min(round_ms), "ms_per_step_max": max(round_ms)},
-            "parity": parity, "nccl_exchange": nccl_exchange,
+            "parity": parity, "nccl_exchange": nccl_exchange, "phases_ms_rank0": phases,
             "exchange_share": 1.0 - ms_gemm / ms_step, "ms_gemm_per_step": ms_gemm,
             "scaling_base": scaling_base,
             "cpu_baseline": None,
@@ -1035,8 +1036,6 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", choices=["peer", "nccl"], default="peer",
                     help="multi-GPU row exchange: peer-memory pushes (default) or NCCL all-to-all")
-    ap.add_argument("--no-overlap", action="store_true",
-                    help="multi-GPU runs: keep both dispatches on the main stream (nothing hidden under the GEMMs)")
     ap.add_argument("--no-parity", action="store_true",
                     help="multi-GPU runs: skip the check against the NCCL path and the fp32 products before timing")
     ap.add_argument("--no-nccl-compare", action="store_true",

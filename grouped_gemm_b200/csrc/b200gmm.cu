@@ -282,8 +282,7 @@ int check_problem(int z, int64_t tokens, int64_t d1, int64_t n, int trans_a, int
   // Tiles are drawn from a global counter.  For wgrad, where a tile's duration is
   // its expert's row count, the experts are taken largest first, so that the
   // CTAs that finish early find short tiles left.
-  p->dynamic = env_int("B200GMM_DYNAMIC", 1) != 0;
-  p->order = (p->dynamic && z > 1 && p->mode == kTN) ? env_int("B200GMM_ORDER", 1) : 0;
+  p->order = (z > 1 && p->mode == kTN) ? 1 : 0;
   // Transposed tiles for experts of at most 64 rows: off unless asked for.  They
   // take 4x fewer tensor-core cycles on such experts, but those experts are bound
   // by streaming their weights from HBM either way, and measured end to end the
@@ -444,7 +443,7 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   // The tile counter of the kernel's scheduler sits in the 16 bytes after the
   // batch_sizes copy and starts every launch at zero.
   uint32_t* sched_counter = reinterpret_cast<uint32_t*>(static_cast<char*>(workspace) + size_t(z) * sizeof(int64_t));
-  if (p.dynamic && cudaMemsetAsync(sched_counter, 0, 16, stream) != cudaSuccess) return B200GMM_ECUDA;
+  if (cudaMemsetAsync(sched_counter, 0, 16, stream) != cudaSuccess) return B200GMM_ECUDA;
 
   const int64_t* bs_dev = batch_sizes;
   if (!batch_sizes_on_device) {

@@ -668,7 +668,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
         int pos = first_tile;
         // Positions after the first come from the global counter, drawn one tile
         // ahead of their use so that the atomic's round trip is never waited for.
-        uint32_t drawn = (p.dynamic && pos < walk.total) ? atomicAdd(sched_counter, 1u) : 0u;
+        uint32_t drawn = (pos < walk.total) ? atomicAdd(sched_counter, 1u) : 0u;
         bool ok = true;
         while (ok) {
           int entry = 0;
@@ -706,12 +706,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           }
           if (!feed.publish(pos, entry)) { ok = false; break; }
           if (!live) break;  // the end of the order has been handed to everyone
-          if (p.dynamic) {
-            pos = static_cast<int>(drawn) + tile_stride;
-            if (pos < walk.total) drawn = atomicAdd(sched_counter, 1u);
-          } else {
-            pos += tile_stride;
-          }
+          pos = static_cast<int>(drawn) + tile_stride;
+          if (pos < walk.total) drawn = atomicAdd(sched_counter, 1u);
         }
       }
       __syncwarp();

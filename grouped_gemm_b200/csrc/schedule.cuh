@@ -50,7 +50,6 @@ struct Problem {
   int group_m;     // row-tiles swept together across the columns (L2 reuse of b)
   int light;       // 1: experts of <= kLightRows rows run as transposed tiles (NN/NT, tile_m 128)
   int order;       // 0: experts in index order.  1: experts sorted by rows, largest first
-  int dynamic;     // 1: CTAs draw positions of the launch order from a global counter
   int64_t wait_ns; // limit of every wait inside the kernel, in nanoseconds
   // Derived on the host so that decoding a tile needs no 64-bit division:
   int nt;          // column tiles of kBlockN: ceil(n / 256)

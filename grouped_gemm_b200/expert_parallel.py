@@ -158,8 +158,7 @@ class PeerExchange:
     """Plan + symmetric buffers for one routing.
 
     Buffers (all in one symmetric allocation per rank, same size on every rank):
-      ``a_grouped``  [cap, h_in]   dispatch target, rows grouped by local expert (two of them,
-                                   used in turn when the next step's dispatch is issued ahead)
+      ``a_grouped``  [cap, h_in]   dispatch target, rows grouped by local expert
       ``g_grouped``  [cap, h_out]  dispatch target for output gradients
       ``out_slots``  [pairs, h_out] combine target, (token, slot) order
       ``da_slots``   [pairs, h_in]  combine target for dgrad rows
@@ -235,7 +234,7 @@ class PeerExchange:
         def align(n):
             return (n + 255) // 256 * 256
         sizes = [self.cap * h_in * esize, self.cap * h_out * esize, self.pairs_cap * h_out * esize,
-                 self.pairs_cap * h_in * esize, self.cap * 16, self.cap * h_in * esize]
+                 self.pairs_cap * h_in * esize, self.cap * 16]
         offs, total = [], 0
         for n in sizes:
             offs.append(total)
@@ -257,9 +256,8 @@ class PeerExchange:
             n = rows * cols * torch.empty(0, dtype=dt).element_size()
             return self._symm[off:off + n].view(dt).view(rows, cols)
 
-        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin, self._t_a2 = (table(o) for o in offs)
+        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin = (table(o) for o in offs)
         self.a_grouped = view(offs[0], self.cap, h_in, dtype)
-        self.a_grouped2 = view(offs[5], self.cap, h_in, dtype)   # second dispatch target, for a dispatch issued ahead
         self.g_grouped = view(offs[1], self.cap, h_out, dtype)
         self.out_slots = view(offs[2], self.pairs_cap, h_out, dtype)
         self.da_slots = view(offs[3], self.pairs_cap, h_in, dtype)
@@ -275,7 +273,6 @@ class PeerExchange:
         self.barrier()
         self.back_rank = origin[: self.local_rows, 0].contiguous()
         self.back_row = origin[: self.local_rows, 1].to(torch.int64).contiguous()
-        self.comm_stream = torch.cuda.Stream(device=device)
         # Final address of every grouped row on the rank that owns its token, for
         # the GEMMs that write their result straight there (step_fused).
         out_bases = self._t_out[self.back_rank.long()]
@@ -284,19 +281,16 @@ class PeerExchange:
         self.dest_da = (da_bases + self.back_row * (h_in * esize)).contiguous()
         self._ws_bytes = _capi.workspace_bytes(self.per_rank)
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
-        self._ahead = None       # (data_ptr of the x dispatched ahead, buffer index, event)
-        self._cur = 0            # which a_grouped buffer the current step reads
-        # Blocks of a push that runs under a GEMM: enough to keep NVLink busy, few
-        # enough to leave the GEMM its memory bandwidth.
-        self.side_push_ctas = 32
+        # step_fused(..., timeline=True) leaves here the CUDA events that bracket its
+        # phases (see phase_times)
+        self._marks = None
 
     # -- plumbing ---------------------------------------------------------------
-    def barrier(self, channel=0):
+    def barrier(self):
         """Every rank's earlier work on the current stream is complete, and visible
-        to its peers, before any rank's later work starts (stream-ordered).  Barriers
-        issued from two streams at once must use different channels."""
+        to its peers, before any rank's later work starts (stream-ordered)."""
         if self.world > 1:
-            self._hdl.barrier(channel=channel)
+            self._hdl.barrier()
 
     def _push(self, src, src_row, dst_rank, dst_row, table, max_ctas=0):
         n_items = int(dst_rank.numel())
@@ -339,7 +333,6 @@ class PeerExchange:
         whatever an earlier step still reads on any rank is done before this one
         overwrites the buffers."""
         self.barrier()
-        self._ahead = None
         a = self.dispatch(x)
         c = gmm_fn(a, w, self.batch_sizes, False, False)
         out_rows = self.combine_rows(c)
@@ -361,74 +354,63 @@ class PeerExchange:
             torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "b200gmm_run_scatter")
 
-    def step_fused(self, x, w, grad_rows, gmm_fn, x_next=None, overlap=True):
-        """``step`` with the exchange folded into and hidden under the GEMMs.  Same
-        results as ``step``, bit for bit.
+    def phase_times(self):
+        """Milliseconds between the marks of the last ``step_fused(timeline=True)``
+        on the stream (synchronises): how long each GEMM ran with whatever it
+        waited for in front of it, the dispatches and the barriers."""
+        if not self._marks:
+            return {}
+        torch.cuda.synchronize(self.device)
+        names = [n for n, _ in self._marks]
+        evs = [e for _, e in self._marks]
+        return {f"{names[i]} -> {names[i + 1]}": evs[i].elapsed_time(evs[i + 1]) for i in range(len(evs) - 1)}
 
-        * Both combines are written by the GEMM epilogues: the forward and the dgrad
-          kernels send each result row straight into the token owner's buffer (over
-          NVLink when the owner is another GPU), so no combine pass exists.
-        * The dispatch of the output gradient does not depend on the forward GEMM and
-          runs under it, on a second stream, with a capped number of blocks
-          (``overlap=False``: on the main stream, before the dgrad GEMM).
-        * ``x_next``: the activations of the NEXT call (a training loop knows them:
-          the next micro-batch).  Their dispatch is issued under this step's wgrad
-          GEMM into the second dispatch buffer; the next call, given the same tensor
-          as ``x``, finds its rows in place and starts with the forward GEMM.
+    def step_fused(self, x, w, grad_rows, gmm_fn, timeline=False):
+        """``step`` with both combines folded into the GEMMs: the forward and the
+        dgrad kernels send each result row from their epilogue straight into the
+        token owner's buffer (over NVLink when the owner is another GPU), so no
+        combine pass exists and only the two dispatches remain as passes of their
+        own.  Same results as ``step``, bit for bit.
+
+        Everything runs on the current stream, one kernel at a time.  (Running the
+        dispatches on a second stream under the GEMMs was built and measured:
+        with a row push sharing the SMs of a GEMM some result rows came out wrong
+        at 4 and 8 GPUs, so nothing here overlaps a GEMM with another kernel.)
 
         Cross-rank order: a barrier on entry (every rank has finished with the
         previous step's buffers), one after each dispatch (its rows have arrived),
         one at the end (the rows the epilogues sent have arrived)."""
         compute = torch.cuda.current_stream(self.device)
-        comm = self.comm_stream
         pairs = self.num_tokens * self.top_k
         rows = self.local_rows
+        marks = [] if timeline else None
+
+        def mark(name):
+            if marks is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record(compute)
+                marks.append((name, ev))
+
+        mark("start")
         self.barrier()
-        entered = compute.record_event()
-        ahead = self._ahead
-        self._ahead = None
-        if ahead is not None and ahead[0] == x.data_ptr():
-            self._cur = ahead[1]
-            dispatched = ahead[2]
-        else:
-            if ahead is not None:
-                compute.wait_event(ahead[2])   # a dispatch nobody claimed: let it finish before its buffer is reused
-            dispatched = None
-        a_buf, a_table = (self.a_grouped, self._t_a) if self._cur == 0 else (self.a_grouped2, self._t_a2)
-        # gradient rows: under the forward GEMM
-        if overlap:
-            with torch.cuda.stream(comm):
-                comm.wait_event(entered)
-                self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g, self.side_push_ctas)
-                self.barrier(channel=1)
-                g_ready = comm.record_event()
-            grad_rows.record_stream(comm)
-        if dispatched is None:
-            self._push(x, self.item_token, self.item_rank, self.item_row, a_table)
-            self.barrier()
-        else:
-            compute.wait_event(dispatched)
-        a = a_buf[:rows]
+        mark("entry barrier")
+        self._push(x, self.item_token, self.item_rank, self.item_row, self._t_a)
+        self.barrier()
+        mark("activations dispatched")
+        a = self.a_grouped[:rows]
         self._gmm_scatter(a, w, self.dest_out, False)
-        if overlap:
-            compute.wait_event(g_ready)
-        else:
-            self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
-            self.barrier()                     # also publishes the forward's rows
+        mark("forward")
+        self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
+        self.barrier()                         # also publishes the forward's rows
+        mark("gradient rows dispatched")
         g = self.g_grouped[:rows]
         self._gmm_scatter(g, w, self.dest_da, True)
-        if x_next is not None:
-            # next step's activations: under the wgrad GEMM, into the other buffer
-            nxt = 1 - self._cur
-            t_next = self._t_a if nxt == 0 else self._t_a2
-            issued = compute.record_event()
-            with torch.cuda.stream(comm):
-                comm.wait_event(issued)
-                self._push(x_next, self.item_token, self.item_rank, self.item_row, t_next, self.side_push_ctas)
-                self.barrier(channel=1)
-                self._ahead = (x_next.data_ptr(), nxt, comm.record_event())
-            x_next.record_stream(comm)
+        mark("dgrad")
         dw = gmm_fn(a, g, self.batch_sizes, True, False)
+        mark("wgrad")
         self.barrier()                         # the rows both epilogues sent have arrived everywhere
+        mark("final barrier")
         dx = self.da_slots[:pairs].view(self.num_tokens, self.top_k, self.h_in).sum(1)
+        mark("top-k sum")
+        self._marks = marks
         return self.out_slots[:pairs], dx, dw

@@ -87,17 +87,11 @@ def test_peer_exchange_single_rank_matches_oracle():
     out_rows, dx, dw = px.step(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
     out_rows, dx, dw = out_rows.clone(), dx.clone(), dw.clone()
     xd, wd, gd = x.cuda(), w.cuda(), grad.cuda()
-    for kwargs in (dict(overlap=False), dict(), dict(x_next=xd), dict(x_next=xd)):
-        # (the last call finds its rows dispatched ahead by the one before)
-        o2, dx2, dw2 = px.step_fused(xd, wd, gd, gmm_fn, **kwargs)
+    for _ in range(2):
+        o2, dx2, dw2 = px.step_fused(xd, wd, gd, gmm_fn, timeline=True)
         torch.cuda.synchronize()
-        assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw), kwargs
-    # rows dispatched ahead for one tensor are not used for another
-    other = (xd.float() * 2).bfloat16()
-    o3, dx3, dw3 = px.step_fused(other, wd, gd, gmm_fn)
-    want3 = px.step(other, wd, gd, gmm_fn)
-    torch.cuda.synchronize()
-    assert all(torch.equal(u, v) for u, v in zip((o3, dx3, dw3), want3))
+        assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw)
+    assert len(px.phase_times()) == 9
     want_rows, want_dx, want_dw = _unsharded_oracle()
     assert _close(out_rows, want_rows) and _close(dx, want_dx, 5e-2) and _close(dw, want_dw, 5e-2)
     assert bool((dw[Z - 1] == 0).all())
@@ -132,20 +126,15 @@ def _worker(rank, world, port, results):
         # Replayed steps reuse the buffers, so the barriers must order them: every
         # iteration gets its own inputs and is compared with its own all-to-all
         # result (an overwrite by a rank that runs ahead would change the output).
-        # Iteration i announces the activations of iteration i + 1.
         xs = [(xl.float() * (1 + 0.25 * i)).bfloat16() for i in range(5)]
         gs = [(gl.float() * (1 - 0.125 * i)).bfloat16() for i in range(5)]
-        for mode in ("pushes", "fused", "fused-no-overlap", "fused-ahead"):
+        for mode in ("pushes", "fused"):
             for i in range(4):
                 want = ep.expert_parallel_step(xs[i], wl, gs[i], plan, gmm_fn)
                 if mode == "pushes":
                     got = px.step(xs[i], wl, gs[i], gmm_fn)
-                elif mode == "fused":
-                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn)
-                elif mode == "fused-no-overlap":
-                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, overlap=False)
                 else:
-                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, x_next=xs[i + 1])
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn)
                 got = [t.clone() for t in got]
                 torch.cuda.synchronize()
                 same = same and all(torch.equal(u, v) for u, v in zip(got, want))
