@@ -176,12 +176,6 @@ int device_info(DeviceInfo** out) {
       (void)cudaGetLastError();
       clusters = 0;
     }
-    // The row-push kernel uses no shared memory, but it asks for the same
-    // (maximum) shared-memory carveout as the GEMM kernels: an SM changes its
-    // carveout only when idle, so with the default carveout a GEMM CTA could not
-    // become resident next to push CTAs that were launched first.
-    (void)cudaFuncSetAttribute(push_rows_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                               cudaSharedmemCarveoutMaxShared);
     d.pair_ctas = 2 * clusters;
     if (d.pair_ctas > (d.sm_count & ~1)) d.pair_ctas = d.sm_count & ~1;
     d.attrs_set = true;
@@ -677,12 +671,8 @@ int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items, const
   const int rc = device_info(&dev);
   if (rc != B200GMM_OK) return rc;
   // Rows are handed out grid-stride to 4 CTAs per SM: enough loads in flight to
-  // fill NVLink and HBM, while leaving thread slots free so that a GEMM kernel
-  // launched on another stream can become resident next to this one (8 CTAs of
-  // 256 threads would fill an SM's 2048 thread slots and lock the GEMM out until
-  // the whole transfer is done).
-  // max_ctas > 0 caps the grid for a transfer that is meant to trickle along under
-  // a GEMM on another stream without taking its memory bandwidth.
+  // fill NVLink and HBM.  max_ctas > 0 caps the grid for a transfer that should
+  // leave memory bandwidth to other work.
   int64_t grid = int64_t(dev->sm_count) * 4;
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
   if (grid > n_items) grid = n_items;

@@ -288,7 +288,7 @@ int b200gmm_run_swiglu_backward(const void* a, const void* b_gate, const void* b
  * memory is only written, never read.  The caller orders the transfer against
  * the consumers on the other GPUs (a barrier after the push).  `max_ctas` > 0
  * caps the number of thread blocks (default: four per SM), for a transfer that
- * should run under a GEMM on another stream rather than compete with it.
+ * should leave memory bandwidth to other work.
  * The reference has no counterpart: it is single-GPU and leaves the
  * sort-by-expert permutation to its callers.
  */
