@@ -733,7 +733,7 @@ def ep_value_single(steps, dev):
     grad = torch.randn(EP["tokens"] * EP["top_k"], EP["ffn"], device=dev, generator=g).bfloat16()
     px = ep.PeerExchange(ids, EP["z"], EP["hidden"], EP["ffn"], single_rank=True)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
-    step = lambda: px.step_fused(x, w, grad, gmm_fn)
+    step = lambda: px.step_fused(x, w, grad, gmm_fn, x_next=x)
     for _ in range(3):
         step()
     steps = max(steps, 2)
@@ -752,8 +752,11 @@ def ep_parity(ep, px, plan, x, w, grad, gmm_fn, backend, rank):
     local GEMMs of this rank against an fp32 CPU product on sampled rows."""
     want = ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
     differs = []
-    for tag in ("step_fused", "step_fused again (buffers reused)"):
-        got = px.step_fused(x, w, grad, gmm_fn)
+    for tag, in_kernel, nxt in (("step_fused", True, None), ("step_fused announcing the next activations", True, x),
+                                ("step_fused on activations sent ahead", True, x),
+                                ("step_fused on activations sent ahead, none announced", True, None),
+                                ("step_fused with the gradient push as its own kernel", False, None)):
+        got = px.step_fused(x, w, grad, gmm_fn, push_in_kernel=in_kernel, x_next=nxt)
         torch.cuda.synchronize()
         for name, u, v in zip(("out_rows", "dx", "dw"), got, want):
             if u.shape != v.shape or not torch.equal(u, v):
@@ -853,7 +856,8 @@ def measure_multi(args):
         if args.no_fused_combine:
             step = lambda: px.step(x, w, grad, gmm_fn)
         else:
-            step = lambda: px.step_fused(x, w, grad, gmm_fn)
+            step = lambda: px.step_fused(x, w, grad, gmm_fn, push_in_kernel=not args.no_push_in_kernel,
+                                         x_next=None if args.no_push_in_kernel else x)
         exchange_step = step
     else:
         step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
@@ -872,7 +876,8 @@ def measure_multi(args):
     # where a step's time goes on this rank's main stream (one more step, marked with events)
     phases = None
     if px is not None and not (args.no_fused_combine):
-        px.step_fused(x, w, grad, gmm_fn, timeline=True)
+        px.step_fused(x, w, grad, gmm_fn, timeline=True, push_in_kernel=not args.no_push_in_kernel,
+                      x_next=None if args.no_push_in_kernel else x)
         phases = px.phase_times()
 
     # the same step with NCCL all-to-all as the exchange (the baseline of this path)
@@ -944,8 +949,11 @@ def measure_multi(args):
                          "peak_source": f"{peaks['source']} cuBLAS bf16 sustained (per GPU)", "traffic": None},
             "exchange": (("peer memory over NVLink (symmetric memory): "
                           + ("4 row pushes per step" if args.no_fused_combine else
-                             "2 row pushes (dispatch) per step, both combines written by the GEMM epilogues "
-                             "straight into the token owners' buffers")
+                             "both combines written by the GEMM epilogues straight into the token owners' buffers; "
+                             + ("2 row pushes (dispatch) per step" if args.no_push_in_kernel else
+                                "the gradient dispatch done by push warps inside the forward GEMM kernel and the "
+                                "next step's activation dispatch by push warps inside the dgrad kernel: no "
+                                "exchange pass of its own is left in a step"))
                           )
                          if args.exchange == "peer" else "NCCL all_to_all_single + index gathers" + exchange_note),
             "rounds": {"count": args.rounds, "ms_per_step_min": min(round_ms), "ms_per_step_max": max(round_ms)},
@@ -1040,6 +1048,9 @@ def main():
                     help="multi-GPU runs: skip the check against the NCCL path and the fp32 products before timing")
     ap.add_argument("--no-nccl-compare", action="store_true",
                     help="multi-GPU runs: skip timing the same step with NCCL all-to-all as the exchange")
+    ap.add_argument("--no-push-in-kernel", action="store_true",
+                    help="multi-GPU runs: dispatch the gradient rows with a row push of its own after the forward "
+                         "GEMM instead of with the push warps inside it")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="multi-GPU runs: combine with separate push kernels instead of from the GEMM epilogues")
     ap.add_argument("--no-scaling-base", action="store_true",

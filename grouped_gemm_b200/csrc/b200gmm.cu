@@ -92,13 +92,14 @@ struct LaunchArgs {
   int64_t a_src_rows = 0;
   int64_t dest_lo = 0, dest_hi = 0;       // window every row_dest entry must fall into (0, 0: unchecked)
   const __nv_bfloat16* gate_grad = nullptr;  // gated product: output gradient, selects the backward epilogue
+  PushArgs push = {};                     // rows to move while the product runs (src == nullptr: none)
 };
 
-template <int MODE, int CTAS, bool GATHER, bool SWIGLU>
+template <int MODE, int CTAS, bool GATHER, bool SWIGLU, bool PUSH = false>
 cudaError_t launch_gmm(const LaunchArgs& a) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(a.grid);
-  cfg.blockDim = dim3(GATHER ? gather_threads<CTAS, MODE>() : kThreads);
+  cfg.blockDim = dim3(GATHER ? gather_threads<CTAS, MODE>() : (PUSH ? kGemmPushThreads : kThreads));
   cfg.dynamicSmemBytes = kSmemBytes;
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
@@ -108,9 +109,18 @@ cudaError_t launch_gmm(const LaunchArgs& a) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, a.map_a, a.map_b, a.map_b2, a.map_c, a.map_a2, a.c,
+  return cudaLaunchKernelEx(&cfg, gmm_kernel<MODE, CTAS, GATHER, SWIGLU, PUSH>, a.map_a, a.map_b, a.map_b2, a.map_c, a.map_a2, a.c,
                             a.batch_sizes, a.p, a.status, a.slots, a.sched_counter, a.row_dest, a.a_rows, a.a_src, a.a_src_rows,
-                            a.row_scale, a.reduce_add, a.dest_lo, a.dest_hi, a.gate_grad);
+                            a.row_scale, a.reduce_add, a.dest_lo, a.dest_hi, a.gate_grad, a.push);
+}
+
+// The plain forward / dgrad kernels with push warps (a.push.src != nullptr).
+cudaError_t launch_with_push(const LaunchArgs& a, int ctas) {
+  if (a.p.mode == kNN)
+    return ctas == 2 ? launch_gmm<kNN, 2, false, false, true>(a) : launch_gmm<kNN, 1, false, false, true>(a);
+  if (a.p.mode == kNT)
+    return ctas == 2 ? launch_gmm<kNT, 2, false, false, true>(a) : launch_gmm<kNT, 1, false, false, true>(a);
+  return cudaErrorInvalidValue;
 }
 
 // The layout (a.p.mode) picks the last template argument; the gated product has no wgrad form.
@@ -127,9 +137,9 @@ cudaError_t launch_variant(const LaunchArgs& a, int ctas) {
   return ctas == 2 ? launch_layout<2, GATHER, SWIGLU>(a) : launch_layout<1, GATHER, SWIGLU>(a);
 }
 
-template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
+template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false, bool PUSH = false>
 cudaError_t set_smem_attr() {
-  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS, GATHER, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS, GATHER, SWIGLU, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(kSmemBytes));
 }
 
@@ -156,7 +166,9 @@ int device_info(DeviceInfo** out) {
         set_smem_attr<kNN, 2, true>() != cudaSuccess || set_smem_attr<kNT, 2, true>() != cudaSuccess ||
         set_smem_attr<kTN, 1, true>() != cudaSuccess || set_smem_attr<kTN, 2, true>() != cudaSuccess ||
         set_smem_attr<kNN, 1, false, true>() != cudaSuccess || set_smem_attr<kNT, 1, false, true>() != cudaSuccess ||
-        set_smem_attr<kNN, 2, false, true>() != cudaSuccess || set_smem_attr<kNT, 2, false, true>() != cudaSuccess)
+        set_smem_attr<kNN, 2, false, true>() != cudaSuccess || set_smem_attr<kNT, 2, false, true>() != cudaSuccess ||
+        set_smem_attr<kNN, 1, false, false, true>() != cudaSuccess || set_smem_attr<kNT, 1, false, false, true>() != cudaSuccess ||
+        set_smem_attr<kNN, 2, false, false, true>() != cudaSuccess || set_smem_attr<kNT, 2, false, false, true>() != cudaSuccess)
       return B200GMM_ECUDA;
     // How many 2-CTA clusters of this kernel the device can hold at once (a GPC
     // with an odd number of free SMs leaves one out).
@@ -364,7 +376,10 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
              uint32_t* device_status, void* cuda_stream, const int64_t* row_dest,
              const int32_t* a_rows = nullptr, int64_t a_source_rows = 0, const void* b2 = nullptr,
              const float* row_scale = nullptr, int reduce_add = 0, const void* dest_base = nullptr,
-             int64_t dest_bytes = 0, const void* gate_grad = nullptr) {
+             int64_t dest_bytes = 0, const void* gate_grad = nullptr, const PushArgs* push = nullptr,
+             bool* push_launched = nullptr) {
+  // push != nullptr: rows to move inside the same launch (plain forward / dgrad
+  // kernels only); *push_launched tells the caller whether a launch took them.
   // gate_grad != nullptr: backward epilogue of the gated product; c is [2, tokens, n].
   if (gate_grad != nullptr && (b2 == nullptr || row_dest != nullptr || (reinterpret_cast<uintptr_t>(gate_grad) & 15)))
     return B200GMM_EINVAL;
@@ -544,13 +559,18 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
     la.a_src = static_cast<const __nv_bfloat16*>(a);
     la.a_src_rows = a_source_rows;
   }
-  const cudaError_t err = gather   ? launch_variant<true, false>(la, ctas)
-                          : swiglu ? launch_variant<false, true>(la, ctas)
-                                   : launch_variant<false, false>(la, ctas);
+  const bool with_push = push != nullptr && push->src != nullptr && push->n_items > 0 && !gather && !swiglu &&
+                         p.mode != kTN;
+  if (with_push) la.push = *push;
+  const cudaError_t err = gather      ? launch_variant<true, false>(la, ctas)
+                          : swiglu    ? launch_variant<false, true>(la, ctas)
+                          : with_push ? launch_with_push(la, ctas)
+                                      : launch_variant<false, false>(la, ctas);
   if (err != cudaSuccess) {
     (void)cudaGetLastError();
     return B200GMM_ECUDA;
   }
+  if (with_push && push_launched != nullptr) *push_launched = true;
   g_launches.fetch_add(1, std::memory_order_relaxed);
   return B200GMM_OK;
 }
@@ -576,6 +596,38 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest, c
   return run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
                   workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr, nullptr, 0,
                   dest_base, dest_bytes);
+}
+
+int b200gmm_run_scatter_push(const void* a, const void* b, const int64_t* row_dest, const void* dest_base,
+                             int64_t dest_bytes, const int64_t* batch_sizes, int batch_sizes_on_device, int z,
+                             int64_t tokens, int64_t dim_a1, int64_t n, int trans_b, const void* push_src,
+                             int64_t push_row_bytes, int64_t push_items, const int32_t* push_src_row,
+                             const int32_t* push_dst_rank, const int64_t* push_dst_row,
+                             const void* const* push_peer_base, void* workspace, size_t workspace_bytes,
+                             uint32_t* device_status, void* cuda_stream) {
+  if (row_dest == nullptr) return B200GMM_EINVAL;
+  if (push_row_bytes <= 0 || (push_row_bytes % 16) != 0 || push_items < 0) return B200GMM_EINVAL;
+  if (push_items > 0) {
+    if (push_src == nullptr || push_dst_rank == nullptr || push_dst_row == nullptr || push_peer_base == nullptr)
+      return B200GMM_EINVAL;
+    if (reinterpret_cast<uintptr_t>(push_src) & 15) return B200GMM_EALIGN;
+  }
+  PushArgs push = {};
+  push.src = static_cast<const uint4*>(push_src);
+  push.row_vecs = push_row_bytes / 16;
+  push.n_items = push_items;
+  push.src_row = push_src_row;
+  push.dst_rank = push_dst_rank;
+  push.dst_row = push_dst_row;
+  push.peer_base = const_cast<void* const*>(push_peer_base);
+  bool pushed = false;
+  const int rc = run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
+                          workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr,
+                          nullptr, 0, dest_base, dest_bytes, nullptr, &push, &pushed);
+  if (rc != B200GMM_OK || pushed || push_items == 0) return rc;
+  // The product was empty and launched nothing: the rows still have to move.
+  return b200gmm_push_rows(push_src, push_row_bytes, push_items, push_src_row, push_dst_rank, push_dst_row,
+                           push_peer_base, 0, cuda_stream);
 }
 
 int b200gmm_run_combine(const void* a, const void* b, const int64_t* row_dest, const void* dest_base,

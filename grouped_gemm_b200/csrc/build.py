@@ -87,7 +87,7 @@ def build_torch_binding(force=False, verbose=False):
     os.makedirs(EXT_BUILD, exist_ok=True)
     load(name=EXT_NAME, sources=[EXT_SRC], extra_include_paths=[os.path.join(ROOT, "include")],
          extra_cflags=["-O2", "-std=c++17"],
-         extra_ldflags=["-L" + HERE, "-lb200gmm", "-Wl,-rpath,$ORIGIN/grouped_gemm_b200/csrc", "-Wl,-rpath," + HERE],
+         extra_ldflags=["-L" + HERE, "-lb200gmm", "-Wl,-rpath,\\$$ORIGIN/grouped_gemm_b200/csrc", "-Wl,-rpath," + HERE],
          build_directory=EXT_BUILD, with_cuda=True, verbose=verbose, is_python_module=False)
     if not os.path.exists(EXT_BUILT):
         raise RuntimeError("torch extension build did not produce " + EXT_BUILT)

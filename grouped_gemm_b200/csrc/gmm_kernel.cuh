@@ -110,6 +110,27 @@ static_assert(kLightWBytes + 2 * kLightXHalf <= Geometry<1>::kStageBytes, "a tra
 template <int CTAS, int MODE = kNN>
 constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS, MODE>::kStages; }
 
+// The push variant adds warps that move rows between GPUs while the tensor cores
+// work: the dispatch that has to precede the NEXT product (e.g. the gradient rows
+// the dgrad product will need, sent while the forward product runs) rides inside
+// this launch instead of being a pass of its own.  The rows are independent of
+// the product: item i is row src_row[i] (or i) of `src` -> row dst_row[i] of the
+// buffer peer_base[dst_rank[i]], exactly what push_rows_kernel moves.  Plain
+// 16-byte loads and stores; remote memory is only written.
+constexpr int kPushWarps = 4;
+constexpr int kGemmPushThreads = kThreads + 32 * kPushWarps;
+constexpr int kPushVecsInFlight = 8;  // 16-byte loads a lane keeps in flight
+
+struct PushArgs {
+  const uint4* src;          // nullptr: nothing to push
+  int64_t row_vecs;          // 16-byte pieces per row
+  int64_t n_items;
+  const int32_t* src_row;    // may be nullptr (item i reads row i)
+  const int32_t* dst_rank;
+  const int64_t* dst_row;
+  void* const* peer_base;
+};
+
 
 struct __align__(8) SmemTail {
   uint64_t full[kMaxStages];
@@ -301,8 +322,8 @@ struct TileFeed {
   }
 };
 
-template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false>
-__global__ void __launch_bounds__(GATHER ? gather_threads<CTAS, MODE>() : kThreads, 1)
+template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false, bool PUSH = false>
+__global__ void __launch_bounds__(GATHER ? gather_threads<CTAS, MODE>() : (PUSH ? kGemmPushThreads : kThreads), 1)
 gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
            const __grid_constant__ CUtensorMap map_b2, const __grid_constant__ CUtensorMap map_c,
            const __grid_constant__ CUtensorMap map_a2, __nv_bfloat16* __restrict__ c,
@@ -310,8 +331,10 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
            uint32_t* status, CUtensorMap* map_slots, uint32_t* sched_counter, const int64_t* __restrict__ row_dest,
            const int32_t* __restrict__ a_rows, const __nv_bfloat16* __restrict__ a_src,
            const int64_t a_src_rows, const float* __restrict__ row_scale, const int reduce_add,
-           const int64_t dest_lo, const int64_t dest_hi, const __nv_bfloat16* __restrict__ gate_grad) {
+           const int64_t dest_lo, const int64_t dest_hi, const __nv_bfloat16* __restrict__ gate_grad,
+           const PushArgs push) {
   static_assert(!SWIGLU || MODE != kTN, "the gated product is a forward product");
+  static_assert(!PUSH || (!GATHER && !SWIGLU && MODE != kTN), "push warps exist in the plain forward / dgrad kernels");
   // SWIGLU: two right operands of n columns each, b (gate) and b2 (up).  The
   // schedule runs over 2n virtual columns, 256 per tile: accumulator columns
   // [0,128) are a @ b[:, c0 .. c0+128), columns [128,256) are a @ b2[:, c0 ..
@@ -712,6 +735,32 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       __syncwarp();
     }
+  } else if (PUSH && warp > kSchedWarp) {
+    // ---------------------------------------------------------- row push
+    // Items are dealt warp by warp over the whole grid.  A lane issues all of its
+    // loads of a sweep (kPushVecsInFlight x 16 bytes) before the first store, so a
+    // warp keeps 4 KiB in flight; the stores are not waited for.  The rows are
+    // complete when the kernel is: the caller's barrier after it publishes them.
+    const int64_t first = int64_t(blockIdx.x) * kPushWarps + (warp - (kSchedWarp + 1));
+    const int64_t step = int64_t(gridDim.x) * kPushWarps;
+    for (int64_t item = first; item < push.n_items; item += step) {
+      const int64_t sr = (push.src_row != nullptr) ? push.src_row[item] : item;
+      const uint4* src = push.src + sr * push.row_vecs;
+      uint4* dst = static_cast<uint4*>(push.peer_base[push.dst_rank[item]]) + push.dst_row[item] * push.row_vecs;
+      for (int64_t base = 0; base < push.row_vecs; base += int64_t(kPushVecsInFlight) * 32) {
+        uint4 r[kPushVecsInFlight];
+#pragma unroll
+        for (int j = 0; j < kPushVecsInFlight; ++j) {
+          const int64_t v = base + j * 32 + lane;
+          if (v < push.row_vecs) r[j] = __ldg(src + v);
+        }
+#pragma unroll
+        for (int j = 0; j < kPushVecsInFlight; ++j) {
+          const int64_t v = base + j * 32 + lane;
+          if (v < push.row_vecs) dst[v] = r[j];
+        }
+      }
+    }
   } else if (GATHER && warp > kSchedWarp) {
     // ---------------------------------------------------------- A-row gather
     // The caller's sort-by-expert fused into the load: row i of the grouped
@@ -853,11 +902,12 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     uint32_t stores = 0;  // TMA stores this warp has issued (lane 0's bulk groups)
     bool ok = true;
     bool bad_dest = false;  // a row_dest entry outside the window the caller declared
-    // A scattered row may only go to a 16-byte aligned address inside [dest_lo, dest_hi)
-    // (dest_hi == 0: the caller vouches for its table, e.g. rows in a peer GPU's buffer).
+    // A scattered row may only go to a 16-byte aligned address (the bulk copies that
+    // carry it need that) inside [dest_lo, dest_hi) (dest_hi == 0: the caller vouches
+    // for the range of its table, e.g. rows in a peer GPU's buffer).
     const int64_t dest_row_bytes = (SWIGLU ? (p.n >> 1) : p.n) * 2;
     auto dest_ok = [&](int64_t addr) {
-      return dest_hi == 0 || (addr >= dest_lo && addr + dest_row_bytes <= dest_hi && (addr & 15) == 0);
+      return (addr & 15) == 0 && (dest_hi == 0 || (addr >= dest_lo && addr + dest_row_bytes <= dest_hi));
     };
     // Buffer for the next TMA store and the wait before it may be written: with two
     // buffers the store before last read this one.

@@ -234,7 +234,7 @@ class PeerExchange:
         def align(n):
             return (n + 255) // 256 * 256
         sizes = [self.cap * h_in * esize, self.cap * h_out * esize, self.pairs_cap * h_out * esize,
-                 self.pairs_cap * h_in * esize, self.cap * 16]
+                 self.pairs_cap * h_in * esize, self.cap * 16, self.cap * h_in * esize]
         offs, total = [], 0
         for n in sizes:
             offs.append(total)
@@ -256,8 +256,9 @@ class PeerExchange:
             n = rows * cols * torch.empty(0, dtype=dt).element_size()
             return self._symm[off:off + n].view(dt).view(rows, cols)
 
-        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin = (table(o) for o in offs)
+        self._t_a, self._t_g, self._t_out, self._t_da, self._t_origin, self._t_a2 = (table(o) for o in offs)
         self.a_grouped = view(offs[0], self.cap, h_in, dtype)
+        self.a_grouped2 = view(offs[5], self.cap, h_in, dtype)   # target of an activation dispatch sent a step ahead
         self.g_grouped = view(offs[1], self.cap, h_out, dtype)
         self.out_slots = view(offs[2], self.pairs_cap, h_out, dtype)
         self.da_slots = view(offs[3], self.pairs_cap, h_in, dtype)
@@ -284,6 +285,9 @@ class PeerExchange:
         # step_fused(..., timeline=True) leaves here the CUDA events that bracket its
         # phases (see phase_times)
         self._marks = None
+        # step_fused(x_next=...): (the tensor whose rows were sent ahead, its version, buffer index)
+        self._ahead = None
+        self._cur = 0            # which a_grouped buffer step_fused reads
 
     # -- plumbing ---------------------------------------------------------------
     def barrier(self):
@@ -304,6 +308,7 @@ class PeerExchange:
     # -- exchanges --------------------------------------------------------------
     def dispatch(self, x):
         """[tokens, h_in] -> this rank's grouped rows [local_rows, h_in]."""
+        self._ahead = None   # rows sent ahead by step_fused may sit in this buffer
         self._push(x, self.item_token, self.item_rank, self.item_row, self._t_a)
         self.barrier()
         return self.a_grouped[: self.local_rows]
@@ -342,17 +347,30 @@ class PeerExchange:
         dx = self.combine_reduce(da)
         return out_rows, dx, dw
 
-    def _gmm_scatter(self, a, w, dest, trans_b):
-        """Local grouped GEMM whose epilogue writes row i to address dest[i]."""
+    def _gmm_scatter(self, a, w, dest, trans_b, push=None):
+        """Local grouped GEMM whose epilogue writes row i to address dest[i].
+        ``push`` = (src, src_row, dst_rank, dst_row, table): rows the same launch
+        moves to their owners with its push warps while the product runs."""
         n = w.shape[1] if trans_b else w.shape[2]
         ws = torch.empty(self._ws_bytes, dtype=torch.uint8, device=self.device)
-        rc = self._lib.b200gmm_run_scatter(
-            a.data_ptr(), w.data_ptr(), dest.data_ptr(), None, 0,   # addresses in peer buffers: table built here
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        if push is None:
+            rc = self._lib.b200gmm_run_scatter(
+                a.data_ptr(), w.data_ptr(), dest.data_ptr(), None, 0,   # addresses in peer buffers: table built here
+                self.batch_sizes.data_ptr(), 1,
+                self.per_rank, a.shape[0], a.shape[1], n, 1 if trans_b else 0,
+                ws.data_ptr(), self._ws_bytes, self._status.data_ptr(), stream)
+            self._check(rc, "b200gmm_run_scatter")
+            return
+        src, src_row, dst_rank, dst_row, table = push
+        rc = self._lib.b200gmm_run_scatter_push(
+            a.data_ptr(), w.data_ptr(), dest.data_ptr(), None, 0,
             self.batch_sizes.data_ptr(), 1,
             self.per_rank, a.shape[0], a.shape[1], n, 1 if trans_b else 0,
-            ws.data_ptr(), self._ws_bytes, self._status.data_ptr(),
-            torch.cuda.current_stream(self.device).cuda_stream)
-        self._check(rc, "b200gmm_run_scatter")
+            src.data_ptr(), src.shape[1] * src.element_size(), int(dst_rank.numel()),
+            0 if src_row is None else src_row.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(), table.data_ptr(),
+            ws.data_ptr(), self._ws_bytes, self._status.data_ptr(), stream)
+        self._check(rc, "b200gmm_run_scatter_push")
 
     def phase_times(self):
         """Milliseconds between the marks of the last ``step_fused(timeline=True)``
@@ -365,17 +383,24 @@ class PeerExchange:
         evs = [e for _, e in self._marks]
         return {f"{names[i]} -> {names[i + 1]}": evs[i].elapsed_time(evs[i + 1]) for i in range(len(evs) - 1)}
 
-    def step_fused(self, x, w, grad_rows, gmm_fn, timeline=False):
+    def step_fused(self, x, w, grad_rows, gmm_fn, timeline=False, push_in_kernel=True, x_next=None):
         """``step`` with both combines folded into the GEMMs: the forward and the
         dgrad kernels send each result row from their epilogue straight into the
         token owner's buffer (over NVLink when the owner is another GPU), so no
-        combine pass exists and only the two dispatches remain as passes of their
-        own.  Same results as ``step``, bit for bit.
+        combine pass exists.  With ``push_in_kernel`` the gradient dispatch is not
+        a pass either: the forward kernel's push warps send the gradient rows to
+        the expert owners while its tensor cores work (``b200gmm_run_scatter_push``),
+        which leaves the activation dispatch as the only pass of its own; and given
+        ``x_next``, the activations of the NEXT call, the dgrad kernel's push warps
+        send those too (into a second buffer), so that the next call, if it is made
+        with that same unmodified tensor, starts its forward product right after
+        its entry barrier.  Same results as ``step``, bit for bit.
 
         Everything runs on the current stream, one kernel at a time.  (Running the
-        dispatches on a second stream under the GEMMs was built and measured:
-        with a row push sharing the SMs of a GEMM some result rows came out wrong
-        at 4 and 8 GPUs, so nothing here overlaps a GEMM with another kernel.)
+        dispatches as kernels of their own on a second stream under the GEMMs was
+        built and measured: with a row push sharing the SMs of a GEMM some result
+        rows came out wrong at 4 and 8 GPUs, so nothing here overlaps a GEMM with
+        another kernel.)
 
         Cross-rank order: a barrier on entry (every rank has finished with the
         previous step's buffers), one after each dispatch (its rows have arrived),
@@ -391,20 +416,38 @@ class PeerExchange:
                 ev.record(compute)
                 marks.append((name, ev))
 
+        ahead, self._ahead = self._ahead, None
+        sent_ahead = ahead is not None and ahead[0] is x and ahead[1] == x._version
+        if sent_ahead:
+            self._cur = ahead[2]
+        a_buf, a_table = (self.a_grouped, self._t_a) if self._cur == 0 else (self.a_grouped2, self._t_a2)
         mark("start")
-        self.barrier()
+        self.barrier()                         # with rows sent ahead: they have arrived from every rank
         mark("entry barrier")
-        self._push(x, self.item_token, self.item_rank, self.item_row, self._t_a)
-        self.barrier()
+        if not sent_ahead:
+            self._push(x, self.item_token, self.item_rank, self.item_row, a_table)
+            self.barrier()
         mark("activations dispatched")
-        a = self.a_grouped[:rows]
-        self._gmm_scatter(a, w, self.dest_out, False)
-        mark("forward")
-        self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
-        self.barrier()                         # also publishes the forward's rows
+        a = a_buf[:rows]
+        if push_in_kernel:
+            self._gmm_scatter(a, w, self.dest_out, False,
+                              push=(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g))
+            mark("forward")
+        else:
+            self._gmm_scatter(a, w, self.dest_out, False)
+            mark("forward")
+            self._push(grad_rows, self.item_pair, self.item_rank, self.item_row, self._t_g)
+        self.barrier()                         # publishes the forward's rows and the gradient rows
         mark("gradient rows dispatched")
         g = self.g_grouped[:rows]
-        self._gmm_scatter(g, w, self.dest_da, True)
+        if x_next is not None and push_in_kernel:
+            nxt = 1 - self._cur
+            self._gmm_scatter(g, w, self.dest_da, True,
+                              push=(x_next, self.item_token, self.item_rank, self.item_row,
+                                    self._t_a if nxt == 0 else self._t_a2))
+            self._ahead = (x_next, x_next._version, nxt)
+        else:
+            self._gmm_scatter(g, w, self.dest_da, True)
         mark("dgrad")
         dw = gmm_fn(a, g, self.batch_sizes, True, False)
         mark("wgrad")

@@ -41,7 +41,7 @@ extern "C" {
 #define B200GMM_STATUS_NEGATIVE_SIZE 0x2u  /* a batch size was < 0 (treated as 0) */
 #define B200GMM_STATUS_ROWS_OVERFLOW 0x4u  /* sum(batch_sizes) > rows of a (clamped) */
 #define B200GMM_STATUS_BAD_ROW_INDEX 0x8u  /* run_gather: a row index outside x (read as zeros) */
-#define B200GMM_STATUS_BAD_ROW_DEST 0x10u  /* a row_dest entry outside [dest_base, +dest_bytes) (row skipped) */
+#define B200GMM_STATUS_BAD_ROW_DEST 0x10u  /* a row_dest entry outside [dest_base, +dest_bytes) or not 16-byte aligned (row skipped) */
 
 /* Largest number of experts b200gmm_run_static accepts (its built-in scratch is
  * sized for this many). */
@@ -158,8 +158,8 @@ int b200gmm_run_static(const void* a, const void* b, void* c,
  * dest_base + dest_bytes, or whose address is not 16-byte aligned is NOT written
  * and B200GMM_STATUS_BAD_ROW_DEST is raised.  Pass the output tensor here
  * whenever the table was computed from indices of unknown provenance.  NULL / 0
- * switches the check off for callers that built the table themselves, e.g. from
- * rows of several peer buffers.  The same pair, with the same meaning, follows
+ * switches the range check off for callers that built the table themselves, e.g.
+ * from rows of several peer buffers; the alignment check always applies.  The same pair, with the same meaning, follows
  * row_dest in b200gmm_run_combine, b200gmm_run_gather and b200gmm_run_swiglu.
  * The reference has no counterpart (single GPU; its callers un-sort the output
  * themselves).
@@ -170,6 +170,30 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
                         int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
                         void* workspace, size_t workspace_bytes,
                         uint32_t* device_status, void* cuda_stream);
+
+/*
+ * b200gmm_run_scatter that also moves rows between GPUs while the product runs:
+ * four extra warps per thread block carry out exactly the transfer
+ * b200gmm_push_rows describes (push_* arguments as there: item i is row
+ * push_src_row[i], or i when that is NULL, of push_src -> row push_dst_row[i] of
+ * the buffer push_peer_base[push_dst_rank[i]]), so a dispatch that the NEXT
+ * product needs - e.g. the gradient rows for dgrad, sent while the forward
+ * product runs - costs no pass of its own and no second kernel shares the SMs.
+ * The pushed rows are independent of the product; they are complete when the
+ * launch is, and the caller orders them against their readers as after
+ * b200gmm_push_rows.  Plain loads and stores only; remote memory is only written.
+ * If the product is empty the rows are moved by b200gmm_push_rows instead.
+ * The reference has no counterpart (single GPU).
+ */
+int b200gmm_run_scatter_push(const void* a, const void* b, const int64_t* row_dest,
+                             const void* dest_base, int64_t dest_bytes,
+                             const int64_t* batch_sizes, int batch_sizes_on_device,
+                             int z, int64_t tokens, int64_t dim_a1, int64_t n, int trans_b,
+                             const void* push_src, int64_t push_row_bytes, int64_t push_items,
+                             const int32_t* push_src_row, const int32_t* push_dst_rank,
+                             const int64_t* push_dst_row, const void* const* push_peer_base,
+                             void* workspace, size_t workspace_bytes,
+                             uint32_t* device_status, void* cuda_stream);
 
 /*
  * b200gmm_run_scatter with the router's weights and the top-k sum folded in:

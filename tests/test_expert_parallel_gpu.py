@@ -87,10 +87,17 @@ def test_peer_exchange_single_rank_matches_oracle():
     out_rows, dx, dw = px.step(x.cuda(), w.cuda(), grad.cuda(), gmm_fn)
     out_rows, dx, dw = out_rows.clone(), dx.clone(), dw.clone()
     xd, wd, gd = x.cuda(), w.cuda(), grad.cuda()
-    for _ in range(2):
-        o2, dx2, dw2 = px.step_fused(xd, wd, gd, gmm_fn, timeline=True)
+    for in_kernel, nxt in ((True, None), (False, None), (True, xd), (True, xd), (True, None)):
+        o2, dx2, dw2 = px.step_fused(xd, wd, gd, gmm_fn, timeline=True, push_in_kernel=in_kernel, x_next=nxt)
         torch.cuda.synchronize()
         assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw)
+    # rows sent ahead are not used for a tensor that changed since, nor for another tensor
+    px.step_fused(xd, wd, gd, gmm_fn, x_next=xd)
+    xd.mul_(2.0)
+    o3 = px.step_fused(xd, wd, gd, gmm_fn)[0].clone()
+    torch.cuda.synchronize()
+    want3 = px.step(xd, wd, gd, gmm_fn)[0]
+    assert torch.equal(o3, want3) and not torch.equal(o3, out_rows)
     assert len(px.phase_times()) == 8  # nine marks, eight intervals
     want_rows, want_dx, want_dw = _unsharded_oracle()
     assert _close(out_rows, want_rows) and _close(dx, want_dx, 5e-2) and _close(dw, want_dw, 5e-2)
@@ -128,13 +135,15 @@ def _worker(rank, world, port, results):
         # result (an overwrite by a rank that runs ahead would change the output).
         xs = [(xl.float() * (1 + 0.25 * i)).bfloat16() for i in range(5)]
         gs = [(gl.float() * (1 - 0.125 * i)).bfloat16() for i in range(5)]
-        for mode in ("pushes", "fused"):
+        for mode in ("pushes", "fused", "fused-separate-push", "fused-ahead"):
             for i in range(4):
                 want = ep.expert_parallel_step(xs[i], wl, gs[i], plan, gmm_fn)
                 if mode == "pushes":
                     got = px.step(xs[i], wl, gs[i], gmm_fn)
+                elif mode == "fused-ahead":   # iteration i announces the activations of iteration i + 1
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, x_next=xs[i + 1])
                 else:
-                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn)
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, push_in_kernel=(mode == "fused"))
                 got = [t.clone() for t in got]
                 torch.cuda.synchronize()
                 same = same and all(torch.equal(u, v) for u, v in zip(got, want))

@@ -475,6 +475,67 @@ def test_gmm_scatter_unsorts_in_the_epilogue(gg, trans_b, on_device):
     util.assert_close(want_rows, gmm_oracle.gmm(a.cpu(), b.cpu(), bs.cpu(), trans_b=trans_b), atol=2e-2, what="rows")
 
 
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("sizes,k,n,items,row_elems", [
+    ([300, 0, 5, 700, 129, 64], 256, 328, 1500, 200),     # several tiles, rows of 400 bytes
+    ([2048, 4096, 512, 1536], 1024, 2048, 9000, 2688),    # many tiles per CTA, rows of 5376 bytes
+    ([3, 1, 0, 2], 64, 72, 4000, 8),                      # product far shorter than the transfer, 16-byte rows
+    ([0, 0, 0], 64, 72, 300, 64),                         # empty product: the rows still move
+])
+def test_run_scatter_push_moves_rows_inside_the_launch(gg, trans_b, sizes, k, n, items, row_elems):
+    """b200gmm_run_scatter_push == b200gmm_run_scatter followed by b200gmm_push_rows,
+    bit for bit, for the product and for the pushed rows (two destination buffers,
+    gathered through a row index); rows nobody names stay untouched."""
+    from grouped_gemm_b200 import _capi
+    lib = _capi.load()
+    torch.manual_seed(31)
+    z, T = len(sizes), sum(sizes)
+    a = torch.randn(max(T, 1), k, device="cuda").bfloat16()[:T]
+    b = (torch.randn(z, n, k, device="cuda") if trans_b else torch.randn(z, k, n, device="cuda")).bfloat16() * 0.1
+    bs = torch.tensor(sizes, dtype=torch.int64, device="cuda")
+    R = T + 5
+    perm = torch.randperm(R, device="cuda")[:T]
+    # the transfer: `items` rows of src, chosen through src_row, to rows of two buffers
+    src = torch.randn(items + 11, row_elems, device="cuda").bfloat16()
+    src_row = torch.randint(0, items + 11, (items,), device="cuda", dtype=torch.int32)
+    dst_rank = torch.randint(0, 2, (items,), device="cuda", dtype=torch.int32)
+    dst_row = torch.randperm(items, device="cuda").to(torch.int64)
+
+    def run(fused):
+        out = torch.full((R, n), 9.0, device="cuda", dtype=torch.bfloat16)
+        bufs = [torch.full((items, row_elems), 5.0, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+        table = torch.tensor([t.data_ptr() for t in bufs], dtype=torch.int64, device="cuda")
+        dest = perm * (n * 2) + out.data_ptr()
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        status = gg.backend.backend.device_status(a.device).data_ptr()
+        stream = torch.cuda.current_stream().cuda_stream
+        head = (a.data_ptr(), b.data_ptr(), dest.data_ptr(), out.data_ptr(), out.numel() * 2, bs.data_ptr(), 1, z,
+                T, k, n, 1 if trans_b else 0)
+        push = (src.data_ptr(), row_elems * 2, items, src_row.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(),
+                table.data_ptr())
+        if fused:
+            rc = lib.b200gmm_run_scatter_push(*head, *push, ws.data_ptr(), ws_bytes, status, stream)
+            assert rc == 0, rc
+        else:
+            rc = lib.b200gmm_run_scatter(*head, ws.data_ptr(), ws_bytes, status, stream)
+            assert rc == 0, rc
+            rc = lib.b200gmm_push_rows(*push, 0, stream)
+            assert rc == 0, rc
+        torch.cuda.synchronize()
+        return out, bufs
+
+    want_out, want_bufs = run(False)
+    got_out, got_bufs = run(True)
+    assert torch.equal(got_out, want_out)
+    for g_, w_ in zip(got_bufs, want_bufs):
+        assert torch.equal(g_, w_)
+    # and the transfer is what it says: row dst_row[i] of buffer dst_rank[i] is row src_row[i] of src
+    for r in range(2):
+        sel = dst_rank == r
+        assert torch.equal(got_bufs[r][dst_row[sel]], src[src_row[sel].long()])
+
+
 def test_randomised_shapes_against_oracle(gg):
     """Seeded random group sizes (tiny, tile-boundary, large, mostly empty), odd
     dimensions, all three layouts, batch sizes on either side: every case against
