@@ -506,6 +506,8 @@ def test_run_scatter_push_moves_rows_inside_the_launch(gg, trans_b, sizes, k, n,
         bufs = [torch.full((items, row_elems), 5.0, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
         table = torch.tensor([t.data_ptr() for t in bufs], dtype=torch.int64, device="cuda")
         dest = perm * (n * 2) + out.data_ptr()
+        if T == 0:   # an empty tensor has no address; the table must still be a pointer
+            dest = torch.zeros(1, dtype=torch.int64, device="cuda")
         ws_bytes = _capi.workspace_bytes(z)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
         status = gg.backend.backend.device_status(a.device).data_ptr()
