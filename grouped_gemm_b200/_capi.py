@@ -24,6 +24,7 @@ STATUS_NEGATIVE_SIZE = 0x2
 STATUS_ROWS_OVERFLOW = 0x4
 STATUS_BAD_ROW_INDEX = 0x8
 STATUS_BAD_ROW_DEST = 0x10
+STATUS_HANDOFF = 0x20
 
 # name -> (restype, argtypes); exactly the symbols include/b200gmm.h declares.
 _c = ctypes

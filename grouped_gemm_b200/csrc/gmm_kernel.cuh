@@ -144,6 +144,8 @@ struct __align__(8) SmemTail {
   uint32_t tiles_done;              // tiles of this cluster whose loads have all landed
   uint32_t tmem_base;
   uint32_t abort_flag;
+  uint32_t handoff_fault;           // a role was handed a position out of order (self-check of the ring)
+  uint32_t role_sum[16];            // per taking warp: count of positions taken (low 8 bits) + 256 * their sum
   int row_start[kMaxExperts + 1];   // exclusive prefix sum of batch_sizes, by expert
   int tile_start[kMaxExperts + 1];  // exclusive prefix sum of tile counts, by position in perm
   uint16_t perm[kMaxExperts];       // expert at each position of the launch order
@@ -279,9 +281,17 @@ struct TileFeed {
   uint32_t taken;   // positions taken (or published) so far
   int map;          // sched_map entry of the position taken last
   bool remote;      // this role sits in the peer CTA: what it reads was written from the leader
+  int last;         // position taken last (-1: none yet)
+  uint32_t sum;     // sum of the positions taken
 
   __device__ TileFeed(SmemTail* tail_, const ptx::WaitCtx& w, bool in_peer = false)
-      : tail(tail_), wait(w), taken(0), map(0), remote(in_peer) {}
+      : tail(tail_), wait(w), taken(0), map(0), remote(in_peer), last(-1), sum(0) {}
+
+  // Leaves this role's tally for the teardown check: every taking role of a CTA
+  // must have been handed the same positions.
+  __device__ __forceinline__ void tally(int warp) {
+    tail->role_sum[warp & 15] = (taken & 0xffu) + (sum << 8);
+  }
 
   // Consumer side, called by every lane of a warp (warp_wide) or by one thread.
   __device__ __forceinline__ int take(bool warp_wide, int lane) {
@@ -294,6 +304,18 @@ struct TileFeed {
     if (!got) return kNoTile;
     const int t = *reinterpret_cast<volatile int*>(&tail->sched_tile[slot]);
     map = *reinterpret_cast<volatile int*>(&tail->sched_map[slot]);
+    // Self-check of the hand-off: positions reach every role in strictly
+    // increasing order.  One that does not is never used: the fault is recorded,
+    // the launch is told to drain, and this role stops (warp-uniformly).
+    bool bad = (t <= last);
+    if (warp_wide) bad = __any_sync(0xffffffffu, bad);
+    if (bad) {
+      tail->handoff_fault = 1u;
+      *wait.abort_flag = 1u;
+      return kNoTile;
+    }
+    last = t;
+    sum += static_cast<uint32_t>(t);
     if (warp_wide) __syncwarp();
     if (!warp_wide || lane == 0) {
       // Both values are in registers: the slot may be overwritten from here on.
@@ -389,6 +411,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       tail->tiles_done = 0u;
       tail->abort_flag = 0u;
+      tail->handoff_fault = 0u;
+      for (int i = 0; i < 16; ++i) tail->role_sum[i] = 0xffffffffu;
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -566,6 +590,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           if (++s == kStages) { s = 0; ph ^= 1u; }
         }
       }
+      feed.tally(warp);
     }
     __syncwarp();
   } else if (warp == 1 && leader) {
@@ -589,7 +614,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       const uint32_t ab = it & 1u, aph = (it >> 1) & 1u;
       ++it;
       const uint32_t te_bar = ptx::smem_u32(&tail->tmem_empty[ab]);
-      if (!ptx::mbar_wait(te_bar, aph ^ 1u, wait)) { ok = false; break; }
+      // (acquire at cluster scope: half of the arrivals come from the other CTA's epilogue warps)
+      if (!ptx::mbar_wait<kPair>(te_bar, aph ^ 1u, wait)) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const uint32_t d_tmem = tmem_base + ab * kBlockN;
       if (kLight && t.kind) {
@@ -624,7 +650,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       for (int kb = 0; kb < nkb; ++kb) {
         const uint32_t f_bar = ptx::smem_u32(&tail->full[s]);
-        if (!ptx::mbar_wait(f_bar, ph, wait)) { ok = false; break; }
+        // (gather variant of a pair: one arrival is the other CTA's gather warp)
+        if (!ptx::mbar_wait<kPair && GATHER>(f_bar, ph, wait)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t sa = stage_base + s * G::kStageBytes;
         const uint32_t sb = sa + G::kABytes;
@@ -660,6 +687,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       }
       __syncwarp();
     }
+    if (lane == 0) feed.tally(warp);
   } else if (warp == 1) {
     // peer CTA of a pair: the leader issues the MMAs for both
   } else if (warp == kSchedWarp) {
@@ -1244,11 +1272,22 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     // Shared memory must outlive the stores that still read it.
     if (lane == 0 || scatter_rows) ptx::bulk_wait_group_all();
     if (bad_dest && status != nullptr) atomicOr(status, 0x10u);
+    if (lane == 0) feed.tally(warp);
     __syncwarp();
   }
 
   // ------------------------------------------------------------ teardown
   __syncthreads();
+  if (threadIdx.x == 0 && status != nullptr) {
+    // Self-check: the producer, the MMA issuer and the eight epilogue warps of a
+    // CTA were handed the same positions (same count, same sum), in order.
+    bool fault = tail->handoff_fault != 0u;
+    if (!tail->abort_flag) {
+      const uint32_t ref = tail->role_sum[0];
+      for (int wq = leader ? 1 : 2; wq < 2 + kEpilogueWarps; ++wq) fault = fault || (tail->role_sum[wq] != ref);
+    }
+    if (fault) atomicOr(status, 0x20u);
+  }
   if (tail->abort_flag) {
     // A wait gave up.  Report it, then give copies and MMAs still in flight time
     // to land before shared memory and TMEM are handed back.

@@ -272,18 +272,20 @@ __device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
   return out;
 }
 
-// Arrive on an mbarrier that may live in the peer CTA (shared::cluster address).
-// Default semantics (release at CTA scope): a cluster-scope release costs a
-// round trip per arrival.
+// Arrive on an mbarrier that may live in the other CTA of the pair
+// (shared::cluster address), with release at CLUSTER scope.  The scope matters:
+// the arrival tells a thread of the other CTA that this thread's earlier
+// accesses are done (it has read a ring slot or an accumulator that the other
+// side will now overwrite, or it has written shared memory the other side will
+// now read).  With the instruction's default, release at CTA scope, nothing
+// orders those accesses against an observer outside this CTA, and under memory
+// pressure a ring slot was seen overwritten before every lane had read it.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-// The same arrival with release at cluster scope: it publishes ordinary stores the
-// arriving thread made to the other CTA's shared memory (st_shared_cluster_u32).
-__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
+// (Same instruction; the name used where ordinary stores to the other CTA's
+// shared memory, st_shared_cluster_u32, are being published.)
+__device__ __forceinline__ void mbar_arrive_release_cluster(uint32_t cluster_bar) { mbar_arrive_cluster(cluster_bar); }
 __device__ __forceinline__ void st_shared_cluster_u32(uint32_t cluster_addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }

@@ -41,6 +41,7 @@ extern "C" {
 #define B200GMM_STATUS_NEGATIVE_SIZE 0x2u  /* a batch size was < 0 (treated as 0) */
 #define B200GMM_STATUS_ROWS_OVERFLOW 0x4u  /* sum(batch_sizes) > rows of a (clamped) */
 #define B200GMM_STATUS_BAD_ROW_INDEX 0x8u  /* run_gather: a row index outside x (read as zeros) */
+#define B200GMM_STATUS_HANDOFF 0x20u       /* self-check: a role of a thread block was handed tile positions out of order */
 #define B200GMM_STATUS_BAD_ROW_DEST 0x10u  /* a row_dest entry outside [dest_base, +dest_bytes) or not 16-byte aligned (row skipped) */
 
 /* Largest number of experts b200gmm_run_static accepts (its built-in scratch is

@@ -538,6 +538,45 @@ def test_run_scatter_push_moves_rows_inside_the_launch(gg, trans_b, sizes, k, n,
         assert torch.equal(got_bufs[r][dst_row[sel]], src[src_row[sel].long()])
 
 
+def test_scatter_push_full_size_under_memory_pressure(gg):
+    """The product with 1.4 GB of rows moved by its push warps while it runs (the
+    size at which a pair of thread blocks once lost the order of its tile
+    hand-off: arrivals on a barrier of the other block have to release at cluster
+    scope): three launches, each bit-identical to the plain product, the pushed
+    rows exact, and no status bit (the hand-off checks itself)."""
+    from grouped_gemm_b200 import _capi
+    lib = _capi.load()
+    z, rows, k, n = 16, 65536, 6144, 10752
+    g = torch.Generator(device="cuda").manual_seed(1)
+    sizes = torch.bincount(torch.randint(0, z, (rows,), generator=torch.Generator().manual_seed(3)), minlength=z)
+    bs = sizes.cuda()
+    a = torch.randn(rows, k, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(z, k, n, device="cuda", generator=g) * 0.02).bfloat16()
+    want = gg.backend.gmm(a, w, bs)
+    src = torch.randn(rows, n, device="cuda", generator=g).bfloat16()
+    src_row = torch.randperm(rows, device="cuda").to(torch.int32)
+    dst_row = torch.randperm(rows, device="cuda").to(torch.int64)
+    dst_rank = torch.zeros(rows, dtype=torch.int32, device="cuda")
+    perm = torch.randperm(rows, device="cuda")
+    ws_bytes = _capi.workspace_bytes(z)
+    status = gg.backend.backend.device_status(a.device).data_ptr()
+    for _ in range(3):
+        out = torch.full((rows, n), 9.0, device="cuda", dtype=torch.bfloat16)
+        dst = torch.full((rows, n), 5.0, device="cuda", dtype=torch.bfloat16)
+        table = torch.tensor([dst.data_ptr()], dtype=torch.int64, device="cuda")
+        dest = perm * (n * 2) + out.data_ptr()
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device="cuda")
+        rc = lib.b200gmm_run_scatter_push(
+            a.data_ptr(), w.data_ptr(), dest.data_ptr(), out.data_ptr(), out.numel() * 2, bs.data_ptr(), 1, z,
+            rows, k, n, 0, src.data_ptr(), n * 2, rows, src_row.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(),
+            table.data_ptr(), ws.data_ptr(), ws_bytes, status, torch.cuda.current_stream().cuda_stream)
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        assert gg.backend.device_status() == 0
+        assert torch.equal(out[perm], want)
+        assert torch.equal(dst[dst_row], src[src_row.long()])
+
+
 def test_randomised_shapes_against_oracle(gg):
     """Seeded random group sizes (tiny, tile-boundary, large, mostly empty), odd
     dimensions, all three layouts, batch sizes on either side: every case against
