@@ -561,7 +561,20 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
   }
   const bool with_push = push != nullptr && push->src != nullptr && push->n_items > 0 && !gather && !swiglu &&
                          p.mode != kTN;
-  if (with_push) la.push = *push;
+  if (with_push) {
+    la.push = *push;
+    // Pace the transfer over a share (B200GMM_PUSH_SPREAD percent, default 50; 0: as
+    // fast as it goes) of the time the product is expected to take at 1 PFLOP/s.
+    const int spread = env_int("B200GMM_PUSH_SPREAD", 50);
+    const double product_ns = 2.0 * double(tokens) * double(dim_a1) * double(n) / 1.0e6;
+    const int64_t warps = int64_t(la.grid) * kPushWarps;
+    const int64_t items_per_warp = (push->n_items + warps - 1) / warps;
+    la.push.interval_ns = (spread > 0 && items_per_warp > 0)
+                              ? static_cast<int64_t>(product_ns * (spread > 100 ? 100 : spread) / 100.0 / double(items_per_warp))
+                              : 0;
+    // (the pacing is a wait like any other: all of it stays inside the wait limit)
+    if (la.push.interval_ns * items_per_warp > p.wait_ns) la.push.interval_ns = p.wait_ns / items_per_warp;
+  }
   const cudaError_t err = gather      ? launch_variant<true, false>(la, ctas)
                           : swiglu    ? launch_variant<false, true>(la, ctas)
                           : with_push ? launch_with_push(la, ctas)
@@ -620,6 +633,7 @@ int b200gmm_run_scatter_push(const void* a, const void* b, const int64_t* row_de
   push.dst_rank = push_dst_rank;
   push.dst_row = push_dst_row;
   push.peer_base = const_cast<void* const*>(push_peer_base);
+  push.interval_ns = 0;
   bool pushed = false;
   const int rc = run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
                           workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr,

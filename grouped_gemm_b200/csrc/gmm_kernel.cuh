@@ -129,6 +129,7 @@ struct PushArgs {
   const int32_t* dst_rank;
   const int64_t* dst_row;
   void* const* peer_base;
+  int64_t interval_ns;       // a push warp starts its j-th item no earlier than j * interval_ns after its first (0: no pacing)
 };
 
 
@@ -769,9 +770,21 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     // loads of a sweep (kPushVecsInFlight x 16 bytes) before the first store, so a
     // warp keeps 4 KiB in flight; the stores are not waited for.  The rows are
     // complete when the kernel is: the caller's barrier after it publishes them.
+    // The transfer is paced over the expected duration of the product: sent as
+    // fast as it goes it saturates NVLink for a few milliseconds, the stores to
+    // the peer back up into the SM's load/store queue, and every barrier poll and
+    // shared-memory store of the GEMM roles queues behind them (measured: the
+    // product then runs longer by the whole duration of the transfer).
     const int64_t first = int64_t(blockIdx.x) * kPushWarps + (warp - (kSchedWarp + 1));
     const int64_t step = int64_t(gridDim.x) * kPushWarps;
+    const uint64_t t0 = ptx::globaltimer_ns();
+    uint64_t due = t0;
     for (int64_t item = first; item < push.n_items; item += step) {
+      if (push.interval_ns > 0) {
+        // bounded: `due` lies at most (items per warp) x interval past t0
+        while (ptx::globaltimer_ns() < due) __nanosleep(500);
+        due += static_cast<uint64_t>(push.interval_ns);
+      }
       const int64_t sr = (push.src_row != nullptr) ? push.src_row[item] : item;
       const uint4* src = push.src + sr * push.row_vecs;
       uint4* dst = static_cast<uint4*>(push.peer_base[push.dst_rank[item]]) + push.dst_row[item] * push.row_vecs;
