@@ -169,7 +169,7 @@ class PeerExchange:
     """
 
     def __init__(self, expert_ids, num_experts, h_in, h_out, group=None, dtype=torch.bfloat16,
-                 single_rank=False):
+                 single_rank=False, interleave_destinations=True):
         from grouped_gemm_b200 import _capi
 
         self._lib = _capi.load()
@@ -224,10 +224,25 @@ class PeerExchange:
         e_sorted = flat[order]
         my_start = (torch.cumsum(counts, 0) - counts)          # start of expert e among this rank's sorted items
         within = torch.arange(order.numel(), device=device) - my_start[e_sorted]
+        item_rank = e_sorted // self.per_rank                                  # owner of the item's expert
+        item_row = my_offset[e_sorted] + within                                # row in the owner's grouped buffer
+        # The push kernels walk the items in order, all thread blocks side by side.  In
+        # expert order that would send every rank's rows to rank 0 first, then to rank 1,
+        # ...: all senders on one receiver's links at a time, and this rank's own rows
+        # (no link at all) in a phase of their own.  So the items are dealt round-robin
+        # over the destinations instead, each rank starting with its right-hand
+        # neighbour: every stretch of items then goes to all destinations at once.
+        if interleave_destinations and self.world > 1:
+            dest_start = torch.cumsum(torch.bincount(item_rank, minlength=self.world), 0)
+            dest_start = dest_start - torch.bincount(item_rank, minlength=self.world)
+            nth = torch.arange(order.numel(), device=device) - dest_start[item_rank]   # n-th item for its destination
+            turn = (item_rank - self.rank - 1) % self.world
+            mix = torch.argsort(nth * self.world + turn)
+            order, item_rank, item_row = order[mix], item_rank[mix], item_row[mix]
         self.item_pair = order.to(torch.int32)                                 # (token*top_k + slot) of each item
         self.item_token = torch.div(order, self.top_k, rounding_mode="floor").to(torch.int32)
-        self.item_rank = (e_sorted // self.per_rank).to(torch.int32)           # owner of the item's expert
-        self.item_row = (my_offset[e_sorted] + within).to(torch.int64)         # row in the owner's grouped buffer
+        self.item_rank = item_rank.to(torch.int32)
+        self.item_row = item_row.to(torch.int64)
         self.n_items = int(order.numel())
 
         # one symmetric allocation, carved into the four buffers + the origin table
@@ -383,24 +398,25 @@ class PeerExchange:
         evs = [e for _, e in self._marks]
         return {f"{names[i]} -> {names[i + 1]}": evs[i].elapsed_time(evs[i + 1]) for i in range(len(evs) - 1)}
 
-    def step_fused(self, x, w, grad_rows, gmm_fn, timeline=False, push_in_kernel=True, x_next=None):
+    def step_fused(self, x, w, grad_rows, gmm_fn, timeline=False, push_in_kernel=False, x_next=None):
         """``step`` with both combines folded into the GEMMs: the forward and the
         dgrad kernels send each result row from their epilogue straight into the
         token owner's buffer (over NVLink when the owner is another GPU), so no
-        combine pass exists.  With ``push_in_kernel`` the gradient dispatch is not
-        a pass either: the forward kernel's push warps send the gradient rows to
-        the expert owners while its tensor cores work (``b200gmm_run_scatter_push``),
-        which leaves the activation dispatch as the only pass of its own; and given
-        ``x_next``, the activations of the NEXT call, the dgrad kernel's push warps
-        send those too (into a second buffer), so that the next call, if it is made
-        with that same unmodified tensor, starts its forward product right after
-        its entry barrier.  Same results as ``step``, bit for bit.
+        combine pass exists and the two dispatches are the only exchange passes.
+        Same results as ``step``, bit for bit.
 
-        Everything runs on the current stream, one kernel at a time.  (Running the
-        dispatches as kernels of their own on a second stream under the GEMMs was
-        built and measured: with a row push sharing the SMs of a GEMM some result
-        rows came out wrong at 4 and 8 GPUs, so nothing here overlaps a GEMM with
-        another kernel.)
+        ``push_in_kernel`` moves the dispatches into the GEMM kernels as well: the
+        forward kernel's push warps send the gradient rows to the expert owners
+        while its tensor cores work (``b200gmm_run_scatter_push``), and given
+        ``x_next``, the activations of the NEXT call, the dgrad kernel's push warps
+        send those (into a second buffer), so that the next call, if it is made with
+        that same unmodified tensor, starts its forward product right after its
+        entry barrier.  Every rank must make the same choice.  It is off by default
+        because it measured no faster on B200 (equal at 2 GPUs, 5 % slower at 4:
+        a product that shares the SM-to-NVLink path with the transfer runs longer
+        by about the duration of the transfer).
+
+        Everything runs on the current stream, one kernel at a time.
 
         Cross-rank order: a barrier on entry (every rank has finished with the
         previous step's buffers), one after each dispatch (its rows have arrived),

@@ -93,9 +93,9 @@ def test_peer_exchange_single_rank_matches_oracle():
         assert torch.equal(o2, out_rows) and torch.equal(dx2, dx) and torch.equal(dw2, dw)
     assert len(px.phase_times()) == 8  # nine marks, eight intervals
     # rows sent ahead are not used for a tensor that changed since, nor for another tensor
-    px.step_fused(xd, wd, gd, gmm_fn, x_next=xd)
+    px.step_fused(xd, wd, gd, gmm_fn, push_in_kernel=True, x_next=xd)
     xd.mul_(2.0)
-    o3 = px.step_fused(xd, wd, gd, gmm_fn)[0].clone()
+    o3 = px.step_fused(xd, wd, gd, gmm_fn, push_in_kernel=True)[0].clone()
     torch.cuda.synchronize()
     want3 = px.step(xd, wd, gd, gmm_fn)[0]
     assert torch.equal(o3, want3) and not torch.equal(o3, out_rows)
@@ -141,7 +141,7 @@ def _worker(rank, world, port, results):
                 if mode == "pushes":
                     got = px.step(xs[i], wl, gs[i], gmm_fn)
                 elif mode == "fused-ahead":   # iteration i announces the activations of iteration i + 1
-                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, x_next=xs[i + 1])
+                    got = px.step_fused(xs[i], wl, gs[i], gmm_fn, push_in_kernel=True, x_next=xs[i + 1])
                 else:
                     got = px.step_fused(xs[i], wl, gs[i], gmm_fn, push_in_kernel=(mode == "fused"))
                 got = [t.clone() for t in got]
