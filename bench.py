@@ -568,7 +568,26 @@ def fused_neighbours(backend, dev, bs, rounds=6):
     out["swiglu"] = compare((
         ("gmm_swiglu", lambda: backend.gmm_swiglu(a, b_gate, b_up, bs, c=c)),
         ("2 gmm + silu * mul", two_launches)))
-    del b_gate, b_up, h1, x, a
+    # the same with its backward: the gated product as an autograd function (products
+    # recomputed in the backward kernel) against two ops.gmm and torch's elementwise ops
+    from grouped_gemm_b200 import fused, ops
+    grad_h = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+    leaves = [t.detach().requires_grad_(True) for t in (a, b_gate, b_up)]
+
+    def fused_fwd_bwd():
+        for t in leaves:
+            t.grad = None
+        fused.gmm_swiglu(leaves[0], leaves[1], leaves[2], bs).backward(grad_h)
+
+    def separate_fwd_bwd():
+        for t in leaves:
+            t.grad = None
+        (F.silu(ops.gmm(leaves[0], leaves[1], bs)) * ops.gmm(leaves[0], leaves[2], bs)).backward(grad_h)
+
+    out["swiglu_fwd_bwd"] = compare((
+        ("fused.gmm_swiglu forward + backward", fused_fwd_bwd),
+        ("2 ops.gmm + silu * mul, forward + backward", separate_fwd_bwd)))
+    del b_gate, b_up, h1, x, a, leaves, grad_h
     # weighted top-2 combine in the epilogue of the down-projection
     a2 = torch.randn(rows, n, device=dev, generator=g).bfloat16()
     b_down = (torch.randn(z, n, k, device=dev, generator=g) * 0.02).bfloat16()
