@@ -752,7 +752,7 @@ def ep_value_single(steps, dev):
     grad = torch.randn(EP["tokens"] * EP["top_k"], EP["ffn"], device=dev, generator=g).bfloat16()
     px = ep.PeerExchange(ids, EP["z"], EP["hidden"], EP["ffn"], single_rank=True)
     gmm_fn = lambda a_, b_, bs_, ta, tb: backend.gmm(a_, b_, bs_, trans_a=ta, trans_b=tb)
-    step = lambda: px.step_fused(x, w, grad, gmm_fn)
+    step = lambda: px.step_fused(x, w, grad, gmm_fn, x_next=x)
     for _ in range(3):
         step()
     steps = max(steps, 2)
@@ -875,8 +875,8 @@ def measure_multi(args):
         if args.no_fused_combine:
             step = lambda: px.step(x, w, grad, gmm_fn)
         else:
-            step = lambda: px.step_fused(x, w, grad, gmm_fn, push_in_kernel=args.push_in_kernel,
-                                         x_next=x if args.push_in_kernel else None)
+            step = lambda: px.step_fused(x, w, grad, gmm_fn, push_in_kernel=not args.no_push_in_kernel,
+                                         x_next=None if args.no_push_in_kernel else x)
         exchange_step = step
     else:
         step = lambda: ep.expert_parallel_step(x, w, grad, plan, gmm_fn)
@@ -895,8 +895,8 @@ def measure_multi(args):
     # where a step's time goes on this rank's main stream (one more step, marked with events)
     phases = None
     if px is not None and not (args.no_fused_combine):
-        px.step_fused(x, w, grad, gmm_fn, timeline=True, push_in_kernel=args.push_in_kernel,
-                      x_next=x if args.push_in_kernel else None)
+        px.step_fused(x, w, grad, gmm_fn, timeline=True, push_in_kernel=not args.no_push_in_kernel,
+                      x_next=None if args.no_push_in_kernel else x)
         phases = px.phase_times()
 
     # the same step with NCCL all-to-all as the exchange (the baseline of this path)
@@ -969,7 +969,7 @@ def measure_multi(args):
             "exchange": (("peer memory over NVLink (symmetric memory): "
                           + ("4 row pushes per step" if args.no_fused_combine else
                              "both combines written by the GEMM epilogues straight into the token owners' buffers; "
-                             + ("2 row pushes (dispatch) per step" if not args.push_in_kernel else
+                             + ("2 row pushes (dispatch) per step" if args.no_push_in_kernel else
                                 "the gradient dispatch done by push warps inside the forward GEMM kernel and the "
                                 "next step's activation dispatch by push warps inside the dgrad kernel: no "
                                 "exchange pass of its own is left in a step"))
@@ -1067,9 +1067,9 @@ def main():
                     help="multi-GPU runs: skip the check against the NCCL path and the fp32 products before timing")
     ap.add_argument("--no-nccl-compare", action="store_true",
                     help="multi-GPU runs: skip timing the same step with NCCL all-to-all as the exchange")
-    ap.add_argument("--push-in-kernel", action="store_true",
-                    help="multi-GPU runs: dispatch the gradient rows (and the next step's activations) with the push "
-                         "warps inside the forward (dgrad) GEMM kernel instead of with row pushes of their own")
+    ap.add_argument("--no-push-in-kernel", action="store_true",
+                    help="multi-GPU runs: dispatch the gradient rows and the activations with row pushes of their own "
+                         "between the GEMMs instead of from inside the forward / dgrad GEMM kernels")
     ap.add_argument("--no-fused-combine", action="store_true",
                     help="multi-GPU runs: combine with separate push kernels instead of from the GEMM epilogues")
     ap.add_argument("--no-scaling-base", action="store_true",

@@ -100,7 +100,7 @@ cudaError_t launch_gmm(const LaunchArgs& a) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(a.grid);
   cfg.blockDim = dim3(GATHER ? gather_threads<CTAS, MODE>() : (PUSH ? kGemmPushThreads : kThreads));
-  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.dynamicSmemBytes = PUSH ? kSmemBytesPush : kSmemBytes;
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -140,7 +140,7 @@ cudaError_t launch_variant(const LaunchArgs& a, int ctas) {
 template <int MODE, int CTAS, bool GATHER = false, bool SWIGLU = false, bool PUSH = false>
 cudaError_t set_smem_attr() {
   return cudaFuncSetAttribute(gmm_kernel<MODE, CTAS, GATHER, SWIGLU, PUSH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              static_cast<int>(kSmemBytes));
+                              static_cast<int>(PUSH ? kSmemBytesPush : kSmemBytes));
 }
 
 // Per-device facts, looked up once.  Index = CUDA device ordinal.
@@ -563,9 +563,11 @@ int run_impl(const void* a, const void* b, void* c, const int64_t* batch_sizes,
                          p.mode != kTN;
   if (with_push) {
     la.push = *push;
-    // Pace the transfer over a share (B200GMM_PUSH_SPREAD percent, default 50; 0: as
-    // fast as it goes) of the time the product is expected to take at 1 PFLOP/s.
-    const int spread = env_int("B200GMM_PUSH_SPREAD", 50);
+    la.push.via_tma = env_int("B200GMM_PUSH_TMA", 1) ? 1 : 0;  // bulk copies measured faster than the register path
+    // Optional pacing: spread the transfer over a share (B200GMM_PUSH_SPREAD percent; default
+    // 0, as fast as it goes, which measured best) of the time the product is expected to
+    // take at 1 PFLOP/s.
+    const int spread = env_int("B200GMM_PUSH_SPREAD", 0);
     const double product_ns = 2.0 * double(tokens) * double(dim_a1) * double(n) / 1.0e6;
     const int64_t warps = int64_t(la.grid) * kPushWarps;
     const int64_t items_per_warp = (push->n_items + warps - 1) / warps;
@@ -634,6 +636,7 @@ int b200gmm_run_scatter_push(const void* a, const void* b, const int64_t* row_de
   push.dst_row = push_dst_row;
   push.peer_base = const_cast<void* const*>(push_peer_base);
   push.interval_ns = 0;
+  push.via_tma = 0;
   bool pushed = false;
   const int rc = run_impl(a, b, nullptr, batch_sizes, batch_sizes_on_device, z, tokens, dim_a1, n, 0, trans_b,
                           workspace, workspace_bytes, device_status, cuda_stream, row_dest, nullptr, 0, nullptr,

@@ -110,13 +110,14 @@ static_assert(kLightWBytes + 2 * kLightXHalf <= Geometry<1>::kStageBytes, "a tra
 template <int CTAS, int MODE = kNN>
 constexpr int gather_threads() { return kThreads + 32 * Geometry<CTAS, MODE>::kStages; }
 
-// The push variant adds warps that move rows between GPUs while the tensor cores
-// work: the dispatch that has to precede the NEXT product (e.g. the gradient rows
-// the dgrad product will need, sent while the forward product runs) rides inside
-// this launch instead of being a pass of its own.  The rows are independent of
-// the product: item i is row src_row[i] (or i) of `src` -> row dst_row[i] of the
-// buffer peer_base[dst_rank[i]], exactly what push_rows_kernel moves.  Plain
-// 16-byte loads and stores; remote memory is only written.
+// The push variant adds four warps that move rows between GPUs while the tensor
+// cores work (in the default, bulk-copy form of the transfer only one of their
+// threads is busy): the dispatch that has to precede the NEXT product (e.g. the
+// gradient rows the dgrad product will need, sent while the forward product runs)
+// rides inside this launch instead of being a pass of its own.  The rows are
+// independent of the product: item i is row src_row[i] (or i) of `src` -> row
+// dst_row[i] of the buffer peer_base[dst_rank[i]], exactly what push_rows_kernel
+// moves.  No multicast; remote memory is only written.
 constexpr int kPushWarps = 4;
 constexpr int kGemmPushThreads = kThreads + 32 * kPushWarps;
 constexpr int kPushVecsInFlight = 8;  // 16-byte loads a lane keeps in flight
@@ -130,7 +131,12 @@ struct PushArgs {
   const int64_t* dst_row;
   void* const* peer_base;
   int64_t interval_ns;       // a push warp starts its j-th item no earlier than j * interval_ns after its first (0: no pacing)
+  int via_tma;               // 1: rows travel global -> shared -> peer as bulk async copies issued by one thread
 };
+// Staging of the bulk-copy form of the transfer: three chunks in flight per thread block.
+constexpr uint32_t kPushChunkBytes = 2048;
+constexpr int kPushChunks = 3;
+constexpr uint32_t kPushStageBytes = kPushChunkBytes * kPushChunks;
 
 
 struct __align__(8) SmemTail {
@@ -147,6 +153,7 @@ struct __align__(8) SmemTail {
   uint32_t abort_flag;
   uint32_t handoff_fault;           // a role was handed a position out of order (self-check of the ring)
   uint32_t role_sum[16];            // per taking warp: count of positions taken (low 8 bits) + 256 * their sum
+  uint64_t push_full[4];            // push variant, bulk-copy form: a staged chunk has landed (kPushChunks used)
   int row_start[kMaxExperts + 1];   // exclusive prefix sum of batch_sizes, by expert
   int tile_start[kMaxExperts + 1];  // exclusive prefix sum of tile counts, by position in perm
   uint16_t perm[kMaxExperts];       // expert at each position of the launch order
@@ -156,6 +163,10 @@ struct __align__(8) SmemTail {
 constexpr size_t kSmemBytes =
     1024 /*alignment slack*/ + Geometry<1>::kRingBytes + Geometry<1>::kOutBytes + sizeof(SmemTail);
 static_assert(kSmemBytes <= 232448, "exceeds the 227 KiB of shared memory a CTA may use");
+// The push variant's staging chunks follow the tail (forward / dgrad layouts only).
+constexpr size_t kPushStageOffset = (sizeof(SmemTail) + 127) / 128 * 128;
+constexpr size_t kSmemBytesPush = kSmemBytes - sizeof(SmemTail) + kPushStageOffset + kPushStageBytes;
+static_assert(kSmemBytesPush <= 232448, "the push variant's staging must fit too");
 static_assert(Geometry<1>::kRingBytes == Geometry<2>::kRingBytes, "both variants use the same ring size");
 static_assert(Geometry<1, kTN>::kRingBytes + Geometry<1, kTN>::kOutBytes <= Geometry<1>::kRingBytes + Geometry<1>::kOutBytes &&
               Geometry<2, kTN>::kRingBytes + Geometry<2, kTN>::kOutBytes <= Geometry<1>::kRingBytes + Geometry<1>::kOutBytes,
@@ -414,6 +425,8 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
       tail->abort_flag = 0u;
       tail->handoff_fault = 0u;
       for (int i = 0; i < 16; ++i) tail->role_sum[i] = 0xffffffffu;
+      if (PUSH)
+        for (int i = 0; i < kPushChunks; ++i) ptx::mbar_init(ptx::smem_u32(&tail->push_full[i]), 1);
       ptx::fence_mbar_init();
     }
     __syncwarp();
@@ -766,15 +779,64 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
     }
   } else if (PUSH && warp > kSchedWarp) {
     // ---------------------------------------------------------- row push
-    // Items are dealt warp by warp over the whole grid.  A lane issues all of its
-    // loads of a sweep (kPushVecsInFlight x 16 bytes) before the first store, so a
-    // warp keeps 4 KiB in flight; the stores are not waited for.  The rows are
-    // complete when the kernel is: the caller's barrier after it publishes them.
-    // The transfer is paced over the expected duration of the product: sent as
-    // fast as it goes it saturates NVLink for a few milliseconds, the stores to
-    // the peer back up into the SM's load/store queue, and every barrier poll and
-    // shared-memory store of the GEMM roles queues behind them (measured: the
-    // product then runs longer by the whole duration of the transfer).
+    // Two forms.  Default: one thread per thread block issues bulk async copies
+    // (below).  Otherwise the four push warps copy through registers: items are
+    // dealt warp by warp over the whole grid, a lane issues all of its loads of a
+    // sweep (kPushVecsInFlight x 16 bytes) before the first store, and the stores are
+    // not waited for.  Either way the rows are complete when the kernel is: the
+    // caller's barrier after it publishes them.  interval_ns > 0 paces the items
+    // over time (measured: no better than sending as fast as it goes).
+    if (push.via_tma) {
+      // Bulk-copy form: one thread moves this thread block's share of the items in
+      // chunks of 2 KiB, global -> shared (completing on an mbarrier) -> peer, three
+      // chunks in flight; no register staging and nothing through the load/store path.
+      if (warp == kSchedWarp + 1 && lane == 0) {
+        const uint32_t stage = ptx::smem_u32(reinterpret_cast<uint8_t*>(tail) + kPushStageOffset);
+        const int64_t row_bytes = push.row_vecs * 16;
+        const int64_t chunks_per_row = (row_bytes + kPushChunkBytes - 1) / kPushChunkBytes;
+        const int64_t my_items = (push.n_items > blockIdx.x) ? (push.n_items - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+        const int64_t total = my_items * chunks_per_row;
+        const uint64_t t0 = ptx::globaltimer_ns();
+        // chunk q of this block's sequence: item blockIdx.x + (q / chunks_per_row) * gridDim.x, piece q % chunks_per_row
+        auto issue_load = [&](int64_t q) {
+          const int64_t it = q / chunks_per_row, piece = q - it * chunks_per_row;
+          if (piece == 0 && push.interval_ns > 0) {
+            const uint64_t due = t0 + static_cast<uint64_t>(it) * static_cast<uint64_t>(push.interval_ns) / kPushWarps;  // this thread has four warps' shares
+            while (ptx::globaltimer_ns() < due) __nanosleep(500);   // bounded: the pacing as a whole stays inside the wait limit
+          }
+          const int64_t item = blockIdx.x + it * int64_t(gridDim.x);
+          const int64_t sr = (push.src_row != nullptr) ? push.src_row[item] : item;
+          const int64_t off = piece * kPushChunkBytes;
+          const uint32_t bytes = static_cast<uint32_t>(row_bytes - off < kPushChunkBytes ? row_bytes - off : kPushChunkBytes);
+          const int b = static_cast<int>(q % kPushChunks);
+          const uint32_t bar = ptx::smem_u32(&tail->push_full[b]);
+          ptx::mbar_arrive_expect_tx(bar, bytes);
+          ptx::bulk_load_1d(stage + b * kPushChunkBytes, reinterpret_cast<const uint8_t*>(push.src + sr * push.row_vecs) + off,
+                            bytes, bar);
+        };
+        bool ok = true;
+        // loads run two chunks ahead of the stores
+        for (int64_t q = 0; q < total && q < kPushChunks - 1; ++q) issue_load(q);
+        for (int64_t q = 0; q < total && ok; ++q) {
+          if (q + kPushChunks - 1 < total) {
+            // the buffer chunk q + 2 will land in was last read by the store of chunk q - 1
+            if (q >= 1) ptx::bulk_wait_group_read<0>();
+            issue_load(q + kPushChunks - 1);
+          }
+          const int b = static_cast<int>(q % kPushChunks);
+          const uint32_t ph = static_cast<uint32_t>((q / kPushChunks) & 1);
+          if (!ptx::mbar_wait(ptx::smem_u32(&tail->push_full[b]), ph, wait)) { ok = false; break; }
+          const int64_t it = q / chunks_per_row, piece = q - it * chunks_per_row;
+          const int64_t item = blockIdx.x + it * int64_t(gridDim.x);
+          const int64_t off = piece * kPushChunkBytes;
+          const uint32_t bytes = static_cast<uint32_t>(row_bytes - off < kPushChunkBytes ? row_bytes - off : kPushChunkBytes);
+          uint8_t* dst = static_cast<uint8_t*>(push.peer_base[push.dst_rank[item]]) + push.dst_row[item] * row_bytes + off;
+          ptx::bulk_store_1d(dst, stage + b * kPushChunkBytes, bytes);
+          ptx::bulk_commit_group();
+        }
+        ptx::bulk_wait_group_all();
+      }
+    } else {
     const int64_t first = int64_t(blockIdx.x) * kPushWarps + (warp - (kSchedWarp + 1));
     const int64_t step = int64_t(gridDim.x) * kPushWarps;
     const uint64_t t0 = ptx::globaltimer_ns();
@@ -801,6 +863,7 @@ gmm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CU
           if (v < push.row_vecs) dst[v] = r[j];
         }
       }
+    }
     }
   } else if (GATHER && warp > kSchedWarp) {
     // ---------------------------------------------------------- A-row gather

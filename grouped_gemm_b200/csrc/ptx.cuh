@@ -158,6 +158,14 @@ __device__ __forceinline__ void tma_store_2d(const void* map, uint32_t src, int 
                : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1)
                : "memory");
 }
+// global -> shared copy of `bytes` contiguous bytes (multiple of 16, both addresses
+// 16-byte aligned) that completes on an mbarrier of this CTA.  No multicast.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
 // shared -> global copy of `bytes` contiguous bytes (multiple of 16, both
 // addresses 16-byte aligned); bulk async group of the issuing thread.  The
 // destination may be memory of another GPU mapped into this process.

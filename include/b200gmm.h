@@ -174,7 +174,9 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
 
 /*
  * b200gmm_run_scatter that also moves rows between GPUs while the product runs:
- * four extra warps per thread block carry out exactly the transfer
+ * extra warps in every thread block (by default one thread of them, issuing bulk
+ * async copies global -> shared -> destination; B200GMM_PUSH_TMA=0: four warps
+ * copying through registers) carry out exactly the transfer
  * b200gmm_push_rows describes (push_* arguments as there: item i is row
  * push_src_row[i], or i when that is NULL, of push_src -> row push_dst_row[i] of
  * the buffer push_peer_base[push_dst_rank[i]]), so a dispatch that the NEXT
@@ -182,7 +184,7 @@ int b200gmm_run_scatter(const void* a, const void* b, const int64_t* row_dest,
  * product runs - costs no pass of its own and no second kernel shares the SMs.
  * The pushed rows are independent of the product; they are complete when the
  * launch is, and the caller orders them against their readers as after
- * b200gmm_push_rows.  Plain loads and stores only; remote memory is only written.
+ * b200gmm_push_rows.  No multicast; remote memory is only written.
  * If the product is empty the rows are moved by b200gmm_push_rows instead.
  * The reference has no counterpart (single GPU).
  */

@@ -475,6 +475,7 @@ def test_gmm_scatter_unsorts_in_the_epilogue(gg, trans_b, on_device):
     util.assert_close(want_rows, gmm_oracle.gmm(a.cpu(), b.cpu(), bs.cpu(), trans_b=trans_b), atol=2e-2, what="rows")
 
 
+@pytest.mark.parametrize("bulk", ["0", "1"], ids=["through-registers", "bulk-copies"])
 @pytest.mark.parametrize("trans_b", [False, True])
 @pytest.mark.parametrize("sizes,k,n,items,row_elems", [
     ([300, 0, 5, 700, 129, 64], 256, 328, 1500, 200),     # several tiles, rows of 400 bytes
@@ -482,11 +483,13 @@ def test_gmm_scatter_unsorts_in_the_epilogue(gg, trans_b, on_device):
     ([3, 1, 0, 2], 64, 72, 4000, 8),                      # product far shorter than the transfer, 16-byte rows
     ([0, 0, 0], 64, 72, 300, 64),                         # empty product: the rows still move
 ])
-def test_run_scatter_push_moves_rows_inside_the_launch(gg, trans_b, sizes, k, n, items, row_elems):
+def test_run_scatter_push_moves_rows_inside_the_launch(gg, monkeypatch, bulk, trans_b, sizes, k, n, items, row_elems):
     """b200gmm_run_scatter_push == b200gmm_run_scatter followed by b200gmm_push_rows,
     bit for bit, for the product and for the pushed rows (two destination buffers,
-    gathered through a row index); rows nobody names stay untouched."""
+    gathered through a row index); rows nobody names stay untouched.  Both forms of
+    the transfer: through registers by four warps, and as bulk copies by one thread."""
     from grouped_gemm_b200 import _capi
+    monkeypatch.setenv("B200GMM_PUSH_TMA", bulk)
     lib = _capi.load()
     torch.manual_seed(31)
     z, T = len(sizes), sum(sizes)
@@ -538,13 +541,15 @@ def test_run_scatter_push_moves_rows_inside_the_launch(gg, trans_b, sizes, k, n,
         assert torch.equal(got_bufs[r][dst_row[sel]], src[src_row[sel].long()])
 
 
-def test_scatter_push_full_size_under_memory_pressure(gg):
+@pytest.mark.parametrize("bulk", ["0", "1"], ids=["through-registers", "bulk-copies"])
+def test_scatter_push_full_size_under_memory_pressure(gg, monkeypatch, bulk):
     """The product with 1.4 GB of rows moved by its push warps while it runs (the
     size at which a pair of thread blocks once lost the order of its tile
     hand-off: arrivals on a barrier of the other block have to release at cluster
     scope): three launches, each bit-identical to the plain product, the pushed
     rows exact, and no status bit (the hand-off checks itself)."""
     from grouped_gemm_b200 import _capi
+    monkeypatch.setenv("B200GMM_PUSH_TMA", bulk)
     lib = _capi.load()
     z, rows, k, n = 16, 65536, 6144, 10752
     g = torch.Generator(device="cuda").manual_seed(1)
