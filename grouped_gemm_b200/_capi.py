@@ -47,6 +47,7 @@ SIGNATURES = {
         _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,
         _c.c_void_p, _c.c_int64, _c.c_int64, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p,
         _c.c_void_p, _c.c_size_t, _c.c_void_p, _c.c_void_p]),
+    "b200gmm_sum_slots": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_int, _c.c_int64, _c.c_void_p]),
     "b200gmm_run_combine": (_c.c_int, [
         _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int64, _c.c_void_p, _c.c_int, _c.c_void_p,
         _c.c_int, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int,

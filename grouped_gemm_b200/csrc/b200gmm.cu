@@ -753,6 +753,25 @@ int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items, const
   return B200GMM_OK;
 }
 
+int b200gmm_sum_slots(const void* slots, void* out, int64_t tokens, int top_k, int64_t cols, void* cuda_stream) {
+  if (tokens < 0 || cols < 0 || top_k < 1 || top_k > kSumMaxTopK || (cols % 8) != 0) return B200GMM_EINVAL;
+  if (tokens == 0 || cols == 0) return B200GMM_OK;
+  if (slots == nullptr || out == nullptr) return B200GMM_EINVAL;
+  if ((reinterpret_cast<uintptr_t>(slots) | reinterpret_cast<uintptr_t>(out)) & 15) return B200GMM_EALIGN;
+  DeviceInfo* dev = nullptr;
+  const int rc = device_info(&dev);
+  if (rc != B200GMM_OK) return rc;
+  const int64_t total = tokens * (cols / 8);
+  int64_t grid = (total + kSumThreads - 1) / kSumThreads;
+  const int64_t cap = int64_t(dev->sm_count) * 16;
+  if (grid > cap) grid = cap;
+  sum_slots_kernel<<<static_cast<unsigned>(grid), kSumThreads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint4*>(slots), static_cast<uint4*>(out), tokens, top_k, cols / 8);
+  if (cudaGetLastError() != cudaSuccess) return B200GMM_ECUDA;
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return B200GMM_OK;
+}
+
 int b200gmm_fill_offsets(const int64_t* batch_sizes_device, int z, int64_t dim_a1, int64_t n,
                          int trans_a, int trans_b, int64_t* out_device, void* cuda_stream) {
   if (trans_a && trans_b) return B200GMM_EINVAL;

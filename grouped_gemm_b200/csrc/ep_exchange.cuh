@@ -13,6 +13,7 @@
 // the inter-GPU transfer in one pass.
 #pragma once
 
+#include <cuda_bf16.h>
 #include <stdint.h>
 
 namespace b200gmm {
@@ -47,6 +48,48 @@ push_rows_kernel(const uint4* __restrict__ src, int64_t row_vecs, int64_t n_item
         if (v < row_vecs) d[v] = r[j];
       }
     }
+  }
+}
+
+// Top-k sum of the combine: out[t, :] = slots[t * top_k, :] + .. + slots[t * top_k +
+// top_k - 1, :], added in fp32 in that order and rounded to bf16 once.  A thread owns
+// 8 columns (16 bytes) of one token; all of its top_k loads are issued before the
+// first add.  HBM-bound: (top_k + 1) x 2 bytes per output element.
+constexpr int kSumThreads = 256;
+constexpr int kSumMaxTopK = 8;
+
+__global__ void __launch_bounds__(kSumThreads)
+sum_slots_kernel(const uint4* __restrict__ slots, uint4* __restrict__ out, int64_t tokens, int top_k,
+                 int64_t row_vecs) {
+  const int64_t total = tokens * row_vecs;
+  for (int64_t i = int64_t(blockIdx.x) * kSumThreads + threadIdx.x; i < total;
+       i += int64_t(gridDim.x) * kSumThreads) {
+    const int64_t t = i / row_vecs, v = i - t * row_vecs;
+    const uint4* src = slots + (t * top_k) * row_vecs + v;
+    uint4 r[kSumMaxTopK];
+#pragma unroll
+    for (int j = 0; j < kSumMaxTopK; ++j)
+      if (j < top_k) r[j] = __ldg(src + int64_t(j) * row_vecs);
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kSumMaxTopK; ++j) {
+      if (j < top_k) {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r[j]);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float2 f = __bfloat1622float2(h[e]);
+          acc[2 * e] += f.x;
+          acc[2 * e + 1] += f.y;
+        }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) ho[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+    out[i] = o;
   }
 }
 

@@ -344,8 +344,19 @@ class PeerExchange:
         """Grouped rows [local_rows, h_in] -> [tokens, h_in], summed over a token's slots."""
         self._push(y, None, self.back_rank, self.back_row, self._t_da)
         self.barrier()
-        slots = self.da_slots[: self.num_tokens * self.top_k]
-        return slots.view(self.num_tokens, self.top_k, self.h_in).sum(1)
+        return self._sum_slots(self.da_slots)
+
+    def _sum_slots(self, slots):
+        """[tokens * top_k, h] per-slot rows -> [tokens, h]: a token's rows added in
+        fp32, rounded once (``b200gmm_sum_slots``)."""
+        h = slots.shape[1]
+        out = torch.empty(self.num_tokens, h, dtype=slots.dtype, device=self.device)
+        if self.top_k > 8 or slots.dtype != torch.bfloat16:
+            return slots[: self.num_tokens * self.top_k].view(self.num_tokens, self.top_k, h).sum(1)
+        rc = self._lib.b200gmm_sum_slots(slots.data_ptr(), out.data_ptr(), self.num_tokens, self.top_k, h,
+                                         torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "b200gmm_sum_slots")
+        return out
 
     def step(self, x, w, grad_rows, gmm_fn):
         """Same unit of work as ``expert_parallel_step``, over peer memory: four
@@ -468,7 +479,7 @@ class PeerExchange:
         mark("wgrad")
         self.barrier()                         # the rows both epilogues sent have arrived everywhere
         mark("final barrier")
-        dx = self.da_slots[:pairs].view(self.num_tokens, self.top_k, self.h_in).sum(1)
+        dx = self._sum_slots(self.da_slots)
         mark("top-k sum")
         self._marks = marks
         return self.out_slots[:pairs], dx, dw

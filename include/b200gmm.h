@@ -325,6 +325,17 @@ int b200gmm_push_rows(const void* src, int64_t row_bytes, int64_t n_items,
                       int max_ctas, void* cuda_stream);
 
 /*
+ * The top-k sum that ends an expert-parallel combine: `slots` is bf16
+ * [tokens * top_k, cols] (the top_k result rows of a token are consecutive),
+ * `out` is bf16 [tokens, cols]; out[t] = slots[t*top_k] + .. + slots[t*top_k +
+ * top_k - 1], added in fp32 in that order, rounded once.  1 <= top_k <= 8, cols a
+ * multiple of 8, both pointers 16-byte aligned device memory.  The reference has
+ * no counterpart (its callers sum the expert outputs of a token themselves).
+ */
+int b200gmm_sum_slots(const void* slots, void* out, int64_t tokens, int top_k,
+                      int64_t cols, void* cuda_stream);
+
+/*
  * Device-side argument fill on its own, for inspection and bit-exact tests:
  * runs the same warp-scan step the GEMM kernels build their schedule from and
  * writes z x B200GMM_FILL_FIELDS int64 values (expert-major) to `out_device`.

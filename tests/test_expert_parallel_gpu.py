@@ -75,6 +75,32 @@ def test_push_rows_permutation_single_gpu():
                                  table.data_ptr(), 0, None) == -1   # rows must be multiples of 16 bytes
 
 
+@pytest.mark.parametrize("tokens,top_k,cols", [(1, 1, 8), (37, 2, 72), (1000, 4, 6144), (513, 8, 264), (0, 4, 64)])
+def test_sum_slots_equals_fp32_sum(tokens, top_k, cols):
+    """b200gmm_sum_slots: a token's top_k rows added in fp32 in slot order and rounded
+    once; bit for bit what an fp32 sum followed by one rounding gives, also with
+    values 2**20 apart in one sum."""
+    from grouped_gemm_b200 import _capi
+    lib = _capi.load()
+    torch.manual_seed(tokens + top_k)
+    slots = torch.randn(tokens * top_k, cols, device="cuda")
+    if tokens:
+        slots[::3] *= 1024.0
+        slots[1::5] *= 2.0 ** -10
+    slots = slots.bfloat16()
+    out = torch.full((tokens, cols), 3.0, device="cuda", dtype=torch.bfloat16)
+    rc = lib.b200gmm_sum_slots(slots.data_ptr() if tokens else 0, out.data_ptr() if tokens else 0, tokens, top_k, cols,
+                               torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    want = torch.zeros(tokens, cols, device="cuda")
+    for j in range(top_k):   # the same order of additions
+        want += slots.view(tokens, top_k, cols)[:, j].float()
+    assert torch.equal(out, want.bfloat16())
+    assert lib.b200gmm_sum_slots(slots.data_ptr(), out.data_ptr(), tokens, 9, cols, 0) != 0       # top_k beyond the limit
+    assert lib.b200gmm_sum_slots(slots.data_ptr(), out.data_ptr(), tokens, top_k, cols + 4, 0) != 0  # cols not a multiple of 8
+
+
 def test_peer_exchange_single_rank_matches_oracle():
     from grouped_gemm_b200 import backend, expert_parallel as ep
     x, w, ids, grad = _problem()
