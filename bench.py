@@ -1034,6 +1034,32 @@ def run_profile_case(args):
         b2 = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
         c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
         fn = lambda: backend.gmm_swiglu(a, b, b2, bs, c=c)
+    elif args.profile == "push":
+        # The forward product with its rows scattered through a table and, inside the same
+        # launch, a row transfer of the size of its output (here into a local buffer: the
+        # kernel is the one the expert-parallel step runs, the destination table has one entry).
+        from grouped_gemm_b200 import _capi
+        lib = _capi.load()
+        a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
+        b = (torch.randn(z, k, n, device=dev, generator=g) * 0.02).bfloat16()
+        c = torch.empty(rows, n, device=dev, dtype=torch.bfloat16)
+        src = torch.randn(rows, n, device=dev, generator=g).bfloat16()
+        dst = torch.empty_like(src)
+        dest = torch.randperm(rows, device=dev) * (n * 2) + c.data_ptr()
+        src_row = torch.randperm(rows, device=dev).to(torch.int32)
+        dst_row = torch.randperm(rows, device=dev).to(torch.int64)
+        dst_rank = torch.zeros(rows, dtype=torch.int32, device=dev)
+        table = torch.tensor([dst.data_ptr()], dtype=torch.int64, device=dev)
+        ws_bytes = _capi.workspace_bytes(z)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        status = backend.backend.device_status(dev).data_ptr()
+
+        def fn():
+            rc = lib.b200gmm_run_scatter_push(
+                a.data_ptr(), b.data_ptr(), dest.data_ptr(), c.data_ptr(), c.numel() * 2, bs.data_ptr(), 1, z, rows, k, n,
+                0, src.data_ptr(), n * 2, rows, src_row.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(),
+                table.data_ptr(), ws.data_ptr(), ws_bytes, status, torch.cuda.current_stream(dev).cuda_stream)
+            _capi.check(rc, "b200gmm_run_scatter_push")
     else:
         a = torch.randn(rows, k, device=dev, generator=g).bfloat16()
         b = torch.randn(rows, n, device=dev, generator=g).bfloat16()
@@ -1048,7 +1074,7 @@ def run_profile_case(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--profile", choices=["fwd", "dgrad", "wgrad", "gather", "swiglu"], default=None,
+    ap.add_argument("--profile", choices=["fwd", "dgrad", "wgrad", "gather", "swiglu", "push"], default=None,
                     help="launch one pass of the Mixtral workload a few times and exit (for ncu)")
     ap.add_argument("--profile-launches", type=int, default=2)
     ap.add_argument("--profile-workload", choices=["mixtral", "down", "fine", "fine64"], default="mixtral")
