@@ -154,6 +154,26 @@ def expert_parallel_step(x, w, grad_rows, plan, gmm_fn, group=None):
 # of the rank that owns the expert (and, on the way back, straight into the
 # token owner's slot-ordered buffer) with ``b200gmm_push_rows`` over NVLink.
 # ---------------------------------------------------------------------------
+def interleave_by_destination(dest, rank, world):
+    """Permutation that deals items round-robin over their destinations.
+
+    ``dest[i]`` is the destination rank of item i.  In the returned order the
+    n-th items of all destinations come before any (n+1)-th item, and within one
+    round the destinations follow each other as rank+1, rank+2, ... (mod world),
+    so that a kernel walking the items in order sends to every destination at
+    once and no two ranks start on the same receiver.  Items of one destination
+    keep their relative order."""
+    dest = dest.to(torch.int64)
+    counts = torch.bincount(dest, minlength=world)
+    # n-th item of its destination, without assuming the items are grouped by destination
+    by_dest = torch.argsort(dest, stable=True)
+    start = torch.cumsum(counts, 0) - counts
+    nth = torch.empty_like(dest)
+    nth[by_dest] = torch.arange(dest.numel(), device=dest.device) - start[dest[by_dest]]
+    turn = (dest - rank - 1) % world
+    return torch.argsort(nth * world + turn, stable=True)
+
+
 class PeerExchange:
     """Plan + symmetric buffers for one routing.
 
@@ -233,11 +253,7 @@ class PeerExchange:
         # over the destinations instead, each rank starting with its right-hand
         # neighbour: every stretch of items then goes to all destinations at once.
         if interleave_destinations and self.world > 1:
-            dest_start = torch.cumsum(torch.bincount(item_rank, minlength=self.world), 0)
-            dest_start = dest_start - torch.bincount(item_rank, minlength=self.world)
-            nth = torch.arange(order.numel(), device=device) - dest_start[item_rank]   # n-th item for its destination
-            turn = (item_rank - self.rank - 1) % self.world
-            mix = torch.argsort(nth * self.world + turn)
+            mix = interleave_by_destination(item_rank, self.rank, self.world)
             order, item_rank, item_row = order[mix], item_rank[mix], item_row[mix]
         self.item_pair = order.to(torch.int32)                                 # (token*top_k + slot) of each item
         self.item_token = torch.div(order, self.top_k, rounding_mode="floor").to(torch.int32)

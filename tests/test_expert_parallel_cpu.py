@@ -108,3 +108,31 @@ def test_single_process_plan_is_identity_exchange():
     assert torch.equal(out_rows, want_rows)
     assert torch.equal(dw, want_dw)
     assert torch.allclose(dx.float(), want_dx, rtol=1e-2, atol=1e-2)
+
+
+def test_interleave_by_destination_round_robin():
+    """The order in which a row push walks its items: a permutation; the n-th items
+    of all destinations before any (n+1)-th; inside a round the destinations follow
+    as rank+1, rank+2, ...; items of one destination keep their order."""
+    import torch
+    from grouped_gemm_b200.expert_parallel import interleave_by_destination
+    g = torch.Generator().manual_seed(7)
+    for world, rank, n in ((2, 0, 11), (4, 1, 257), (8, 7, 1000), (4, 3, 0), (3, 2, 5)):
+        dest = torch.randint(0, world, (n,), generator=g)
+        if n > 20:
+            dest[dest == 2 % world] = (rank + 1) % world       # one destination gets (almost) nothing
+        mix = interleave_by_destination(dest, rank, world)
+        assert sorted(mix.tolist()) == list(range(n))
+        d = dest[mix].tolist()
+        seen = [0] * world
+        prev_key = -1
+        for i, dst in zip(mix.tolist(), d):
+            key = seen[dst] * world + (dst - rank - 1) % world   # (round, turn inside the round)
+            assert key > prev_key
+            prev_key = key
+            seen[dst] += 1
+        for r in range(world):                                   # stable inside a destination
+            mine = [i for i in mix.tolist() if dest[i] == r]
+            assert mine == sorted(mine)
+        if n >= world and all(c > 0 for c in torch.bincount(dest, minlength=world).tolist()):
+            assert d[:world] == [(rank + 1 + j) % world for j in range(world)]
